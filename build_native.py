@@ -5,7 +5,10 @@
   libllmctl_host.so : C++ host runtime (KV block manager, batch scheduler, ...), no CUDA needed
 
 Sources are compiled one translation unit per nvcc/g++ process (in parallel) and only when the
-source or a header is newer than the object, so incremental rebuilds take seconds.  The reference
+source or a header is newer than the object, so incremental rebuilds take seconds.  ``--components serve``
+builds only what inference needs (GEMMs, norms, rotations, activations, attention over the paged caches,
+mixture-of-experts, sampling); entry points of the parts left out are simply absent from the library
+(``ops.native.has_symbol``), and a later full build adds them.  The reference
 has no build system at all — nothing to mirror here.
 """
 from __future__ import annotations
@@ -34,6 +37,25 @@ NVCC_FLAGS = [
 CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall", "-I", str(ROOT / "include")]
 
 
+#: sub-directories (or single files) of csrc/ per component; None = everything
+COMPONENTS = {
+    "serve": ["common", "gemm", "norm", "rope", "swiglu", "activation", "moe", "serve", "attention/latent_attention.cu"],
+    "all": None,
+}
+
+
+def _component_sources(components) -> list[Path]:
+    every = sorted(p for p in CSRC.rglob("*.cu"))
+    if not components or "all" in components:
+        return every
+    keep: set[Path] = set()
+    for c in components:
+        for entry in COMPONENTS[c] or []:
+            q = CSRC / entry
+            keep.update([q] if q.is_file() else q.rglob("*.cu"))
+    return [p for p in every if p in keep]
+
+
 def find_nvcc() -> str | None:
     for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
         if cand and Path(cand).exists():
@@ -58,14 +80,21 @@ def _compile(cmd: list[str], src: Path, obj: Path, verbose: bool) -> tuple[Path,
     return obj, (r.stdout + r.stderr) if verbose else ""
 
 
-def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False, jobs: int | None = None) -> dict:
+def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False, jobs: int | None = None,
+          components=None) -> dict:
     LIBDIR.mkdir(parents=True, exist_ok=True)
     hdr_m = _newest_header_mtime()
     nvcc = find_nvcc()
     out: dict = {}
 
     # ---- CUDA kernels ----
-    cu_srcs = sorted(p for p in CSRC.rglob("*.cu"))
+    cu_srcs = _component_sources(components)
+    manifest = LIBDIR / "libllmctl_b200.sources"
+    linked = set(manifest.read_text().split("\n")) if manifest.exists() and (LIBDIR / "libllmctl_b200.so").exists() else set()
+    wanted = {str(p.relative_to(CSRC)) for p in cu_srcs}
+    if wanted < linked:           # a fuller library is there already: keep it whole and refresh what is stale
+        cu_srcs = sorted(CSRC / rel for rel in linked if (CSRC / rel).exists())
+        wanted = {str(p.relative_to(CSRC)) for p in cu_srcs}
     if cu_srcs:
         if nvcc is None:
             raise RuntimeError("nvcc not found; cannot build libllmctl_b200.so")
@@ -85,12 +114,13 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False, 
                 if log.strip():
                     print(f"--- {obj.name}\n{log}")
         lib = LIBDIR / "libllmctl_b200.so"
-        if tasks or not lib.exists():
+        if tasks or not lib.exists() or wanted != linked:
             cmd = [nvcc, "-shared", "-o", str(lib), *map(str, objs), "-gencode",
                    "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC", "-cudart", "shared"]
             r = subprocess.run(cmd, capture_output=True, text=True)
             if r.returncode != 0:
                 raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+            manifest.write_text("\n".join(sorted(wanted)))
         out["kernels"] = str(lib)
 
     # ---- host C++ ----
@@ -123,8 +153,10 @@ if __name__ == "__main__":
     ap.add_argument("--verbose", action="store_true")
     ap.add_argument("--ptxas-info", action="store_true", help="pass -Xptxas -v (registers/spills/smem)")
     ap.add_argument("-j", type=int, default=None)
+    ap.add_argument("--components", nargs="*", default=None, choices=sorted(COMPONENTS),
+                    help="build only these parts of the kernel library (default: all)")
     a = ap.parse_args()
-    res = build(force=a.force, verbose=a.verbose, ptxas_info=a.ptxas_info, jobs=a.j)
+    res = build(force=a.force, verbose=a.verbose, ptxas_info=a.ptxas_info, jobs=a.j, components=a.components)
     for k, v in res.items():
         print(f"built {k}: {v}")
     sys.exit(0)

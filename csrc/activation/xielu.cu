@@ -1,0 +1,61 @@
+// Elementwise activations of the feed-forward layers, for bf16 or fp32 activations, evaluated in fp32:
+//
+//   xIELU        : z > 0 :  a_pos * z^2 + z / 2          a_pos = softplus(p)
+//                  z <= 0:  a_neg * (exp(z) - 1 - z) + z / 2,   a_neg = 1/2 + softplus(q)
+//                  (the caller passes a_pos and a_neg; they depend on two learned numbers only)
+//   gated SiLU   : out = silu(gate) * up on a packed [rows, 2F] activation (gate first) of either type
+//                  (csrc/swiglu/swiglu.cu is the bf16-only training kernel with a backward).
+// Reference: none (the reference has no model code).
+#include "../common/dtype.cuh"
+
+namespace llmctl {
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+xielu_kernel(const T* __restrict__ z, T* __restrict__ out, long long n, float a_pos, float a_neg) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float v = to_f32(z[i]);
+    const float r = v > 0.f ? a_pos * v * v + 0.5f * v : a_neg * (expm1f(v) - v) + 0.5f * v;
+    out[i] = from_f32<T>(r);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+gated_silu_kernel(const T* __restrict__ gu, long long ld, T* __restrict__ out, int rows, int F) {
+  const long long n = static_cast<long long>(rows) * F;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / F;
+    const int c = static_cast<int>(i % F);
+    const float g = to_f32(gu[r * ld + c]), u = to_f32(gu[r * ld + F + c]);
+    out[i] = from_f32<T>(g / (1.f + expf(-g)) * u);
+  }
+}
+
+static inline int grid_for(long long n) {
+  long long b = (n + 255) / 256;
+  if (b > kNumSMs * 16) b = kNumSMs * 16;
+  return static_cast<int>(b);
+}
+
+}  // namespace llmctl
+
+using namespace llmctl;
+
+LLMCTL_API int llmctl_xielu(const void* z, void* out, int is_fp32, long long n, float a_pos, float a_neg, void* stream) {
+  LLMCTL_BEGIN();
+  if (n == 0) return 0;
+  LLMCTL_DISPATCH_DTYPE(is_fp32, T, (xielu_kernel<T><<<grid_for(n), 256, 0, (cudaStream_t)stream>>>((const T*)z, (T*)out, n, a_pos, a_neg)));
+  LLMCTL_RETURN_LAST();
+}
+
+LLMCTL_API int llmctl_gated_silu(const void* gate_up, long long ld, void* out, int is_fp32, int rows, int F, void* stream) {
+  LLMCTL_BEGIN();
+  LLMCTL_REQUIRE(ld >= 2LL * F);
+  if (rows == 0 || F == 0) return 0;
+  LLMCTL_DISPATCH_DTYPE(is_fp32, T, (gated_silu_kernel<T><<<grid_for(static_cast<long long>(rows) * F), 256, 0, (cudaStream_t)stream>>>(
+                                        (const T*)gate_up, ld, (T*)out, rows, F)));
+  LLMCTL_RETURN_LAST();
+}

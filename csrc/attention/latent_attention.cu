@@ -1,0 +1,301 @@
+// Latent (low-rank joint key/value) attention over a paged cache, for prompts, portions of prompts and decoded
+// tokens in one ragged batch; bf16 or fp32 activations and cache, all attention arithmetic in fp32.
+//
+// What is cached per token is ONE row shared by all heads: [ c (R numbers: the RMS-normed latent) | kr (dr numbers:
+// the rotated key part) ].  The per-head keys and values are linear images of c (k_h = Uk_h c, v_h = Uv_h c), so
+//
+//     score(i, j, h) = (Uk_h^T qn_ih) . c_j  +  qr_ih . kr_j          out_ih = Uv_h * sum_j p_ij c_j
+//
+// The caller folds Uk_h into the query ("absorbed" query ql = Uk_h^T qn, R numbers) and applies Uv_h to the
+// kernel's output; the kernel therefore is multi-query attention with key width R + dr and value width R read
+// straight from the cache rows, and nothing per head is ever materialised for past tokens.
+//
+//   llmctl_latent_kv_write  : per token, RMS norm (vector weight) of the query latent; RMS norm of the key/value
+//                             latent and interleaved-pair rotation of the shared key part, written to the token's
+//                             cache slot (fused norm + rotation + append).
+//   llmctl_latent_attention : a CTA owns up to 16 query rows = (token, head) pairs of ONE sequence, so a key tile
+//                             is loaded once for 16 tokens of a prompt portion (one head) or for 16 heads of a
+//                             decoded token.  Keys stream through shared memory in tiles of 32 with an online
+//                             softmax; the rotated query part is rotated on load.  Causal: a row at position p
+//                             sees cache positions 0..p of its sequence.  Long contexts are split over CTAs
+//                             (`splits` > 1) and merged by a second kernel, as the decode kernel in
+//                             csrc/serve/paged_attention.cu does.
+// Reference: none (the reference re-runs the HF model over the whole sequence, reference llmctl/serve/server.py:199-204).
+#include "../common/dtype.cuh"
+#include "../rope/rope_interleaved.cuh"
+
+namespace llmctl {
+
+// d: [tokens, ld] = [ q latent raw (Q) | kv latent raw (R) | key rope part raw (dr) ] (R = dr = 0 columns absent for
+// a layer that reads another layer's cache).
+template <typename T>
+__global__ void __launch_bounds__(128)
+latent_kv_write_kernel(const T* __restrict__ d, long long ld, int Q, int R, int dr, const T* __restrict__ wq,
+                       const T* __restrict__ wkv, T* __restrict__ cq, T* __restrict__ cache,
+                       const long long* __restrict__ slots, const int* __restrict__ positions,
+                       const float* __restrict__ freq, float mult, float eps) {
+  __shared__ float red[32];
+  const long long tok = blockIdx.x;
+  const T* row = d + tok * ld;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < Q; c += blockDim.x) {
+    const float v = to_f32(row[c]);
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float rq = 1.f / sqrtf(ss / static_cast<float>(Q) + eps);
+  for (int c = threadIdx.x; c < Q; c += blockDim.x) cq[tok * Q + c] = from_f32<T>(to_f32(row[c]) * rq * to_f32(wq[c]));
+  if (R == 0) return;
+  const long long slot = slots[tok];
+  if (slot < 0) return;  // padded token: uniform over the block, nobody waits below
+  float sk = 0.f;
+  for (int c = threadIdx.x; c < R; c += blockDim.x) {
+    const float v = to_f32(row[Q + c]);
+    sk += v * v;
+  }
+  sk = block_sum(sk, red);
+  const float rk = 1.f / sqrtf(sk / static_cast<float>(R) + eps);
+  T* dst = cache + slot * (R + dr);
+  for (int c = threadIdx.x; c < R; c += blockDim.x) dst[c] = from_f32<T>(to_f32(row[Q + c]) * rk * to_f32(wkv[c]));
+  const T* kr = row + Q + R;
+  const int pos = positions[tok];
+  for (int c = threadIdx.x; c < dr; c += blockDim.x)
+    dst[R + c] = from_f32<T>(rope_interleaved_coord([&](int k) { return to_f32(kr[k]); }, c, pos, freq, mult));
+}
+
+constexpr int kRows = 16;      // query rows per CTA
+constexpr int kKeys = 32;      // keys per tile
+constexpr int kAttnThreads = 128;
+
+// tiles: int32 [ntiles, 4] = {first token row, token count, sequence row (block table), unused}
+// ql: fp32 [tokens, H, R] absorbed queries;  q: [tokens, ldq] raw queries, head h at h * (dn + dr), rope part last
+// out: [tokens, H, R] (T) if gridDim.z == 1, else partial fp32 [tokens, H, splits, R + 2] = {acc, max, sum}
+template <typename T, int NC>
+__global__ void __launch_bounds__(kAttnThreads)
+latent_attention_kernel(const float* __restrict__ ql, const T* __restrict__ q, long long ldq, int dn,
+                        const T* __restrict__ cache, const int* __restrict__ block_tables, int max_blocks,
+                        int block_size, const int* __restrict__ tiles, const int* __restrict__ positions,
+                        const float* __restrict__ freq, float mult, float scale, int H, int R, int dr, int heads_per_tile,
+                        int keys_per_split, T* __restrict__ out, float* __restrict__ partial) {
+  extern __shared__ float smem[];
+  const int D = R + dr, Dp = D + 1;
+  float* qs = smem;                      // [kRows][Dp]
+  float* ks = qs + kRows * Dp;           // [kKeys][Dp]
+  float* ps = ks + kKeys * Dp;           // [kRows][kKeys]
+  float* row_m = ps + kRows * kKeys;     // [kRows]
+  float* row_l = row_m + kRows;
+  float* row_c = row_l + kRows;
+  int* row_pos = reinterpret_cast<int*>(row_c + kRows);
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int* tile = tiles + 4 * blockIdx.x;
+  const int tok0 = tile[0], ntok = tile[1], seq = tile[2];
+  const int h0 = blockIdx.y * heads_per_tile;
+  const int nh = min(heads_per_tile, H - h0);
+  const int nrows = ntok * nh;           // row r -> token tok0 + r / nh, head h0 + r % nh
+  const int split = blockIdx.z, nsplit = gridDim.z;
+  const int* bt = block_tables + static_cast<long long>(seq) * max_blocks;
+
+  if (tid < kRows) {
+    row_m[tid] = -INFINITY;
+    row_l[tid] = 0.f;
+    row_c[tid] = 1.f;
+    row_pos[tid] = tid < nrows ? positions[tok0 + tid / nh] : -1;
+  }
+  __syncthreads();
+  for (int idx = tid; idx < kRows * D; idx += kAttnThreads) {
+    const int r = idx / D, c = idx % D;
+    float v = 0.f;
+    if (r < nrows) {
+      const int tok = tok0 + r / nh, h = h0 + r % nh;
+      if (c < R) {
+        v = ql[(static_cast<long long>(tok) * H + h) * R + c];
+      } else {
+        const T* qr = q + tok * ldq + static_cast<long long>(h) * (dn + dr) + dn;
+        v = rope_interleaved_coord([&](int k) { return to_f32(qr[k]); }, c - R, row_pos[r], freq, mult);
+      }
+    }
+    qs[r * Dp + c] = v * scale;
+  }
+  float acc[kRows][NC];
+#pragma unroll
+  for (int r = 0; r < kRows; ++r)
+#pragma unroll
+    for (int i = 0; i < NC; ++i) acc[r][i] = 0.f;
+
+  const int last = row_pos[nrows - 1];                     // positions grow with the token index
+  const int k_begin = split * keys_per_split;
+  const int k_end = min(last + 1, k_begin + keys_per_split);
+  for (int j0 = k_begin; j0 < k_end; j0 += kKeys) {
+    __syncthreads();                                       // previous tile fully consumed (and qs written)
+    for (int idx = tid; idx < kKeys * D; idx += kAttnThreads) {
+      const int jj = idx / D, c = idx % D, j = j0 + jj;
+      float v = 0.f;
+      if (j < k_end) {
+        const long long slot = static_cast<long long>(bt[j / block_size]) * block_size + (j % block_size);
+        v = to_f32(cache[slot * D + c]);
+      }
+      ks[jj * Dp + c] = v;
+    }
+    __syncthreads();
+    {   // scores: thread -> row tid % 16, keys tid / 16 + 8 * i
+      const int r = tid & 15;
+      const float* qr = qs + r * Dp;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int jj = (tid >> 4) + 8 * i;
+        const float* kr = ks + jj * Dp;
+        float s = 0.f;
+        for (int c = 0; c < D; ++c) s += qr[c] * kr[c];
+        const int j = j0 + jj;
+        ps[r * kKeys + jj] = (j < k_end && j <= row_pos[r]) ? s : -INFINITY;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < kRows / 4; ++i) {   // online softmax: warp w owns rows 4w .. 4w+3, one key per lane
+      const int r = warp * (kRows / 4) + i;
+      const float s = ps[r * kKeys + lane];
+      const float m_old = row_m[r];
+      const float m_new = fmaxf(m_old, warp_max(s));
+      const float p = (m_new == -INFINITY) ? 0.f : expf(s - m_new);
+      const float corr = (m_new == -INFINITY) ? 1.f : expf(m_old - m_new);
+      const float sum = warp_sum(p);
+      ps[r * kKeys + lane] = p;
+      if (lane == 0) {
+        row_m[r] = m_new;
+        row_l[r] = row_l[r] * corr + sum;
+        row_c[r] = corr;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < NC; ++i) {
+      const int c = tid + i * kAttnThreads;
+      if (c < R) {
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) acc[r][i] *= row_c[r];
+        for (int jj = 0; jj < kKeys; ++jj) {
+          const float kv = ks[jj * Dp + c];
+#pragma unroll
+          for (int r = 0; r < kRows; ++r) acc[r][i] += ps[r * kKeys + jj] * kv;
+        }
+      }
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < kRows; ++r) {
+    if (r >= nrows) continue;
+    const int tok = tok0 + r / nh, h = h0 + r % nh;
+    const long long base = static_cast<long long>(tok) * H + h;
+    if (nsplit == 1) {
+      const float inv = row_l[r] > 0.f ? 1.f / row_l[r] : 0.f;
+#pragma unroll
+      for (int i = 0; i < NC; ++i) {
+        const int c = tid + i * kAttnThreads;
+        if (c < R) out[base * R + c] = from_f32<T>(acc[r][i] * inv);
+      }
+    } else {
+      float* dst = partial + (base * nsplit + split) * (R + 2);
+#pragma unroll
+      for (int i = 0; i < NC; ++i) {
+        const int c = tid + i * kAttnThreads;
+        if (c < R) dst[c] = acc[r][i];
+      }
+      if (tid == 0) {
+        dst[R] = row_m[r];
+        dst[R + 1] = row_l[r];
+      }
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+latent_attention_merge_kernel(const float* __restrict__ partial, T* __restrict__ out, int R, int nsplit) {
+  const long long base = blockIdx.x;   // token * H + head
+  const float* p = partial + base * nsplit * (R + 2);
+  float gm = -INFINITY;
+  for (int s = 0; s < nsplit; ++s) gm = fmaxf(gm, p[s * (R + 2) + R]);
+  float gl = 0.f;
+  for (int s = 0; s < nsplit; ++s) {
+    const float ms = p[s * (R + 2) + R];
+    if (ms != -INFINITY) gl += p[s * (R + 2) + R + 1] * expf(ms - gm);
+  }
+  const float inv = gl > 0.f ? 1.f / gl : 0.f;
+  for (int c = threadIdx.x; c < R; c += blockDim.x) {
+    float a = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+      const float ms = p[s * (R + 2) + R];
+      if (ms != -INFINITY) a += p[s * (R + 2) + c] * expf(ms - gm);
+    }
+    out[base * R + c] = from_f32<T>(a * inv);
+  }
+}
+
+template <typename T>
+static int launch_latent_attention(const float* ql, const void* q, long long ldq, int dn, const void* cache,
+                                   const int* block_tables, int max_blocks, int block_size, const int* tiles, int ntiles,
+                                   const int* positions, const float* freq, float mult, float scale, int H, int R, int dr,
+                                   int heads_per_tile, int splits, int keys_per_split, void* out, float* partial,
+                                   int tokens, cudaStream_t s) {
+  const int D = R + dr;
+  const size_t smem = (static_cast<size_t>(kRows + kKeys) * (D + 1) + kRows * kKeys + 4 * kRows) * sizeof(float);
+  if (smem > 227 * 1024) return static_cast<int>(cudaErrorInvalidValue);
+  const int nc = (R + kAttnThreads - 1) / kAttnThreads;
+  dim3 grid(ntiles, (H + heads_per_tile - 1) / heads_per_tile, splits);
+#define LAUNCH(NC)                                                                                                   \
+  do {                                                                                                               \
+    auto kern = latent_attention_kernel<T, NC>;                                                                      \
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
+    if (e != cudaSuccess) return static_cast<int>(e);                                                                \
+    kern<<<grid, kAttnThreads, smem, s>>>(ql, (const T*)q, ldq, dn, (const T*)cache, block_tables, max_blocks,       \
+                                          block_size, tiles, positions, freq, mult, scale, H, R, dr, heads_per_tile, \
+                                          keys_per_split, (T*)out, partial);                                         \
+  } while (0)
+  if (nc <= 1) LAUNCH(1);
+  else if (nc <= 2) LAUNCH(2);
+  else if (nc <= 4) LAUNCH(4);
+  else if (nc <= 8) LAUNCH(8);
+  else return static_cast<int>(cudaErrorInvalidValue);
+#undef LAUNCH
+  if (splits > 1)
+    latent_attention_merge_kernel<T><<<tokens * H, 128, 0, s>>>(partial, (T*)out, R, splits);
+  return 0;
+}
+
+}  // namespace llmctl
+
+using namespace llmctl;
+
+LLMCTL_API int llmctl_latent_kv_write(const void* d, long long ld, int Q, int R, int dr, const void* wq, const void* wkv,
+                                      void* cq, void* cache, const long long* slots, const int* positions,
+                                      const float* freq, float mult, float eps, int tokens, int is_fp32, void* stream) {
+  LLMCTL_BEGIN();
+  LLMCTL_REQUIRE(Q > 0 && R >= 0 && dr >= 0 && dr % 2 == 0 && ld >= Q + R + dr);
+  if (tokens == 0) return 0;
+  LLMCTL_DISPATCH_DTYPE(is_fp32, T, (latent_kv_write_kernel<T><<<tokens, 128, 0, (cudaStream_t)stream>>>(
+                                        (const T*)d, ld, Q, R, dr, (const T*)wq, (const T*)wkv, (T*)cq, (T*)cache, slots,
+                                        positions, freq, mult, eps)));
+  LLMCTL_RETURN_LAST();
+}
+
+// partial: fp32 scratch of tokens * H * splits * (R + 2) numbers when splits > 1 (may be null otherwise).
+LLMCTL_API int llmctl_latent_attention(const float* ql, const void* q, long long ldq, int dn, const void* cache,
+                                       const int* block_tables, int max_blocks, int block_size, const int* tiles,
+                                       int ntiles, int tokens, const int* positions, const float* freq, float mult,
+                                       float scale, int H, int R, int dr, int heads_per_tile, int splits,
+                                       int keys_per_split, void* out, float* partial, int is_fp32, void* stream) {
+  LLMCTL_BEGIN();
+  LLMCTL_REQUIRE(H > 0 && R > 0 && dr >= 0 && dr % 2 == 0 && block_size > 0 && heads_per_tile >= 1 &&
+                 heads_per_tile <= kRows && splits >= 1 && keys_per_split > 0 && (splits == 1 || partial != nullptr));
+  if (ntiles == 0) return 0;
+  int rc;
+  LLMCTL_DISPATCH_DTYPE(is_fp32, T, (rc = launch_latent_attention<T>(ql, q, ldq, dn, cache, block_tables, max_blocks, block_size,
+                                                                     tiles, ntiles, positions, freq, mult, scale, H, R, dr,
+                                                                     heads_per_tile, splits, keys_per_split, out, partial,
+                                                                     tokens, (cudaStream_t)stream)));
+  if (rc != 0) LLMCTL_FAIL(rc, "latent attention launch");
+  LLMCTL_RETURN_LAST();
+}

@@ -1,0 +1,229 @@
+// Mixture-of-experts feed-forward: routing, token permutation, grouped expert GEMMs and the weighted combine, with no
+// host synchronisation anywhere (expert loads stay on the device).  bf16 or fp32 activations / weights; router
+// arithmetic, accumulators and the combine are fp32.
+//
+//   llmctl_moe_route   : per token, logits = Wr x (fp32), score = sigmoid or softmax over experts, the `top` largest
+//                        (ties: lowest index), optionally renormalised to sum 1; optional per-token gate
+//                        sigmoid(wg . x) of a shared expert; counts tokens per expert.
+//   llmctl_moe_plan    : one CTA: per-expert row offsets in the permuted buffer, every expert's segment padded to a
+//                        multiple of the GEMM's row tile, and the tile -> expert map.
+//   llmctl_moe_permute : copies every (token, choice) pair's input row into its expert's segment, multiplied by the
+//                        routing weight when the weight applies to the expert's INPUT (scale_input), and records
+//                        where it went.
+//   llmctl_grouped_gemm: out[row, :] = A[row, :] W[expert(row)]^T over the permuted rows; a CTA computes a 64 x 64 tile
+//                        of one expert (row tiles never straddle experts thanks to the padding).
+//   llmctl_moe_combine : y[t] = sum_k (w_k if the weight applies to the OUTPUT) * expert_out[row(t, k)]
+//                               + gate[t] * shared_out[t], in a fixed order (deterministic), fp32.
+// Reference: none (the reference has no model code).
+#include "../common/dtype.cuh"
+
+namespace llmctl {
+
+constexpr int kTileM = 64, kTileN = 64, kTileK = 16;
+
+// x: fp32 [tokens, W] (the residual stream); wr: [E, W]; wg: [W] or null.
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const float* __restrict__ x, const T* __restrict__ wr, const T* __restrict__ wg, int W, int E, int top,
+                 int softmax_scores, int renormalise, int* __restrict__ ids, float* __restrict__ weights,
+                 float* __restrict__ gate, int* __restrict__ counts) {
+  extern __shared__ float score[];   // [E]
+  const long long tok = blockIdx.x;
+  const float* xr = x + tok * W;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  for (int e = warp; e < E + (wg ? 1 : 0); e += nwarp) {
+    const T* w = e < E ? wr + static_cast<long long>(e) * W : wg;
+    float s = 0.f;
+    for (int c = lane; c < W; c += 32) s += xr[c] * to_f32(w[c]);
+    s = warp_sum(s);
+    if (lane == 0) {
+      if (e < E) score[e] = s;
+      else gate[tok] = 1.f / (1.f + expf(-s));
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (softmax_scores) {
+      float m = -INFINITY, z = 0.f;
+      for (int e = 0; e < E; ++e) m = fmaxf(m, score[e]);
+      for (int e = 0; e < E; ++e) z += (score[e] = expf(score[e] - m));
+      for (int e = 0; e < E; ++e) score[e] /= z;
+    } else {
+      for (int e = 0; e < E; ++e) score[e] = 1.f / (1.f + expf(-score[e]));
+    }
+    float total = 0.f;
+    for (int k = 0; k < top; ++k) {
+      int best = 0;
+      float bv = -INFINITY;
+      for (int e = 0; e < E; ++e)
+        if (score[e] > bv) {
+          bv = score[e];
+          best = e;
+        }
+      ids[tok * top + k] = best;
+      weights[tok * top + k] = bv;
+      total += bv;
+      score[best] = -INFINITY;
+      atomicAdd(&counts[best], 1);
+    }
+    if (renormalise)
+      for (int k = 0; k < top; ++k) weights[tok * top + k] /= total;
+  }
+}
+
+// meta: int32 [2 * E + 2 + max_tiles] = { offsets[E] | cursor[E] | num_tiles | padded rows | tile_expert[max_tiles] }
+__global__ void moe_plan_kernel(const int* __restrict__ counts, int E, int* __restrict__ meta, int max_tiles) {
+  if (threadIdx.x != 0) return;
+  int* offsets = meta;
+  int* cursor = meta + E;
+  int* tile_expert = meta + 2 * E + 2;
+  int row = 0, tile = 0;
+  for (int e = 0; e < E; ++e) {
+    offsets[e] = row;
+    cursor[e] = 0;
+    const int nt = (counts[e] + kTileM - 1) / kTileM;
+    for (int i = 0; i < nt && tile < max_tiles; ++i) tile_expert[tile++] = e;
+    row += nt * kTileM;
+  }
+  meta[2 * E] = tile;
+  meta[2 * E + 1] = row;
+}
+
+// One CTA per (token, choice).  dst rows of a segment beyond the expert's count are never read back.
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_permute_kernel(const float* __restrict__ x, int W, const int* __restrict__ ids, const float* __restrict__ weights,
+                   int scale_input, int* __restrict__ meta, int E, int top, int* __restrict__ pair_row, T* __restrict__ xs) {
+  __shared__ int s_row;
+  const long long pair = blockIdx.x;
+  if (threadIdx.x == 0) {
+    const int e = ids[pair];
+    s_row = meta[e] + atomicAdd(&meta[E + e], 1);
+    pair_row[pair] = s_row;
+  }
+  __syncthreads();
+  const long long tok = pair / top;
+  const float w = scale_input ? weights[pair] : 1.f;
+  const float* src = x + tok * W;
+  T* dst = xs + static_cast<long long>(s_row) * W;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) dst[c] = from_f32<T>(w * src[c]);
+}
+
+// A: [padded rows, K] (row stride lda); Wt: [E, N, K] contiguous; out: [padded rows, N].
+// 256 threads, each a 4 x 4 block of the 64 x 64 tile; fp32 accumulation whatever T.
+template <typename T>
+__global__ void __launch_bounds__(256)
+grouped_gemm_kernel(const T* __restrict__ A, long long lda, const T* __restrict__ Wt, T* __restrict__ out, long long ldo,
+                    int N, int K, const int* __restrict__ meta, int E) {
+  const int tile = blockIdx.x;
+  if (tile >= meta[2 * E]) return;
+  const int e = meta[2 * E + 2 + tile];
+  const long long row0 = static_cast<long long>(tile) * kTileM;
+  const int n0 = blockIdx.y * kTileN;
+  const T* Bw = Wt + static_cast<long long>(e) * N * K;
+  __shared__ float As[kTileK][kTileM + 4];
+  __shared__ float Bs[kTileK][kTileN + 4];
+  const int tid = threadIdx.x;
+  const int tr = (tid / 16) * 4, tc = (tid % 16) * 4;
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < K; k0 += kTileK) {
+    for (int idx = tid; idx < kTileM * kTileK; idx += 256) {
+      const int r = idx / kTileK, k = idx % kTileK;
+      As[k][r] = (k0 + k < K) ? to_f32(A[(row0 + r) * lda + k0 + k]) : 0.f;
+      const int n = n0 + r;
+      Bs[k][r] = (k0 + k < K && n < N) ? to_f32(Bw[static_cast<long long>(n) * K + k0 + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < kTileK; ++k) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        a[i] = As[k][tr + i];
+        b[i] = Bs[k][tc + i];
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] += a[i] * b[j];
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (n0 + tc + j < N) out[(row0 + tr + i) * ldo + n0 + tc + j] = from_f32<T>(acc[i][j]);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const T* __restrict__ expert_out, int W, const int* __restrict__ pair_row,
+                   const float* __restrict__ weights, int top, int scale_output, const T* __restrict__ shared_out,
+                   const float* __restrict__ gate, float* __restrict__ y) {
+  const long long tok = blockIdx.x;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    float a = 0.f;
+    for (int k = 0; k < top; ++k) {
+      const float v = to_f32(expert_out[static_cast<long long>(pair_row[tok * top + k]) * W + c]);
+      a += scale_output ? weights[tok * top + k] * v : v;
+    }
+    if (shared_out) a += (gate ? gate[tok] : 1.f) * to_f32(shared_out[tok * W + c]);
+    y[tok * W + c] = a;
+  }
+}
+
+}  // namespace llmctl
+
+using namespace llmctl;
+
+LLMCTL_API int llmctl_moe_tile_rows() { return kTileM; }
+
+LLMCTL_API int llmctl_moe_route(const float* x, const void* wr, const void* wg, int is_fp32, int tokens, int W, int E, int top,
+                                int softmax_scores, int renormalise, int* ids, float* weights, float* gate, int* counts,
+                                void* stream) {
+  LLMCTL_BEGIN();
+  LLMCTL_REQUIRE(E >= 1 && top >= 1 && top <= E && E <= 8192 && (wg == nullptr || gate != nullptr));
+  cudaStream_t s = (cudaStream_t)stream;
+  LLMCTL_CHECK(cudaMemsetAsync(counts, 0, sizeof(int) * E, s));
+  if (tokens == 0) return 0;
+  LLMCTL_DISPATCH_DTYPE(is_fp32, T, (moe_route_kernel<T><<<tokens, 128, E * sizeof(float), s>>>(
+                                        x, (const T*)wr, (const T*)wg, W, E, top, softmax_scores, renormalise, ids, weights, gate, counts)));
+  LLMCTL_RETURN_LAST();
+}
+
+LLMCTL_API int llmctl_moe_plan(const int* counts, int E, int* meta, int max_tiles, void* stream) {
+  LLMCTL_BEGIN();
+  moe_plan_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(counts, E, meta, max_tiles);
+  LLMCTL_RETURN_LAST();
+}
+
+LLMCTL_API int llmctl_moe_permute(const float* x, int W, const int* ids, const float* weights, int scale_input, int* meta,
+                                  int E, int* pair_row, void* xs, int is_fp32, int tokens, int top, void* stream) {
+  LLMCTL_BEGIN();
+  if (tokens == 0) return 0;
+  LLMCTL_DISPATCH_DTYPE(is_fp32, T, (moe_permute_kernel<T><<<tokens * top, 128, 0, (cudaStream_t)stream>>>(
+                                        x, W, ids, weights, scale_input, meta, E, top, pair_row, (T*)xs)));
+  LLMCTL_RETURN_LAST();
+}
+
+LLMCTL_API int llmctl_grouped_gemm(const void* A, long long lda, const void* Wt, void* out, long long ldo, int N, int K,
+                                   const int* meta, int E, int max_tiles, int is_fp32, void* stream) {
+  LLMCTL_BEGIN();
+  LLMCTL_REQUIRE(N > 0 && K > 0 && lda >= K && ldo >= N);
+  if (max_tiles == 0) return 0;
+  dim3 grid(max_tiles, (N + kTileN - 1) / kTileN);
+  LLMCTL_DISPATCH_DTYPE(is_fp32, T, (grouped_gemm_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>(
+                                        (const T*)A, lda, (const T*)Wt, (T*)out, ldo, N, K, meta, E)));
+  LLMCTL_RETURN_LAST();
+}
+
+LLMCTL_API int llmctl_moe_combine(const void* expert_out, int W, const int* pair_row, const float* weights, int top,
+                                  int scale_output, const void* shared_out, const float* gate, float* y, int tokens,
+                                  int is_fp32, void* stream) {
+  LLMCTL_BEGIN();
+  if (tokens == 0) return 0;
+  LLMCTL_DISPATCH_DTYPE(is_fp32, T, (moe_combine_kernel<T><<<tokens, 256, 0, (cudaStream_t)stream>>>(
+                                        (const T*)expert_out, W, pair_row, weights, top, scale_output, (const T*)shared_out, gate, y)));
+  LLMCTL_RETURN_LAST();
+}

@@ -1,1 +1,2 @@
-
+"""Model families.  Importing the package registers every architecture (``models/registry.py``)."""
+from . import nafazen as _nafazen  # noqa: F401  (registers "Nafazen")

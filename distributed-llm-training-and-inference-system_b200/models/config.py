@@ -148,11 +148,15 @@ def get_preset(name: str) -> ModelConfig:
     return ModelConfig.from_dict(PRESETS[name].to_dict())
 
 
-def resolve_model(spec: str | Path | Dict[str, Any] | ModelConfig) -> ModelConfig:
-    """Accept a preset name, a JSON/TOML path, a dict, or a ModelConfig."""
-    if isinstance(spec, ModelConfig):
+def resolve_model(spec: str | Path | Dict[str, Any] | ModelConfig):
+    """Accept a preset name, a JSON/TOML path, a checkpoint directory, a dict, or a configuration object (ModelConfig
+    or the configuration class of an architecture registered in ``models/registry.py``)."""
+    from . import registry
+    if isinstance(spec, ModelConfig) or registry.architecture_of(spec) is not None:
         return spec
     if isinstance(spec, dict):
+        if "architecture" in spec and registry.architecture_named(spec["architecture"]) is not None:
+            return registry.architecture_named(spec["architecture"]).config_from_dict(spec)
         return ModelConfig.from_dict(spec)
     p = Path(str(spec))
     if p.exists() and p.is_file():
@@ -160,7 +164,14 @@ def resolve_model(spec: str | Path | Dict[str, Any] | ModelConfig) -> ModelConfi
     if p.exists() and p.is_dir() and (p / "model_config.json").exists():
         return ModelConfig.from_file(p / "model_config.json")
     if p.exists() and p.is_dir() and (p / "config.json").exists():
-        return from_hf_config(json.loads((p / "config.json").read_text()), name=p.name)
+        raw = json.loads((p / "config.json").read_text())
+        if "architecture" in raw:                       # a design registered in models/registry.py
+            from . import registry
+            arch = registry.architecture_named(raw["architecture"])
+            if arch is None:
+                raise ValueError(f"unknown architecture {raw['architecture']!r}; known: {registry.architecture_names()}")
+            return arch.config_from_dict(raw)
+        return from_hf_config(raw, name=p.name)
     if p.exists() and p.is_dir():
         raise FileNotFoundError(f"{p} has neither model_config.json nor an HF config.json")
     return get_preset(str(spec))

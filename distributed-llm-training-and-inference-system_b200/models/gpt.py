@@ -211,6 +211,12 @@ def build_model(cfg: ModelConfig, *, dtype=torch.bfloat16, device=None, layer_ra
     """Deterministic construction: the RNG is seeded per (seed, tp_rank, first layer) so a TP/PP-sharded
     build is reproducible run to run."""
     st = get_state()
+    from . import registry
+    arch = registry.architecture_of(cfg)
+    if arch is not None:          # a registered design other than the GPT/LLaMA family
+        if layer_range is not None or st.tp > 1:
+            raise ValueError(f"{arch.name} models run unsharded (no tensor or pipeline parallelism)")
+        return arch.build(cfg, dtype=dtype, device=device if device is not None else st.device, seed=seed)
     lo = 0 if layer_range is None else layer_range[0]
     dev = device if device is not None else st.device
     gen_state = torch.random.get_rng_state()

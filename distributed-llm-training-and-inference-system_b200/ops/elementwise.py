@@ -1,0 +1,141 @@
+"""Inference-side elementwise / normalisation ops that exist for bf16 AND fp32 activations: post-norm residual
+update with a single gain, scalar-gain RMS norm of selected rows, scaled embedding lookup, logit soft-capping, xIELU
+and gated SiLU, plus the frequency spectrum of interleaved-pair rotary embeddings (plain or YaRN-blended).
+CUDA tensors run the kernels in csrc/norm/scalar_rmsnorm.cu and csrc/activation/xielu.cu; CPU tensors run the
+PyTorch restatement below (CPU tests).  Sums, gains and the residual stream are fp32 in both.
+
+Reference: none — the reference has no model code (reference llmctl/runtime/engine.py:119-140 loads HF models)."""
+from __future__ import annotations
+
+import math
+from typing import Any, Dict, Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+from . import native
+
+c_void_p, c_int, c_ll, c_float = native.c_void_p, native.c_int, native.c_ll, native.c_float
+native.register_signature("llmctl_postnorm_residual", [c_void_p, c_int, c_ll, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p])
+native.register_signature("llmctl_scalar_rmsnorm", [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p])
+native.register_signature("llmctl_embed_scale", [c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_int, c_int, c_void_p])
+native.register_signature("llmctl_softcap", [c_void_p, c_ll, c_float, c_void_p])
+native.register_signature("llmctl_xielu", [c_void_p, c_void_p, c_int, c_ll, c_float, c_float, c_void_p])
+native.register_signature("llmctl_gated_silu", [c_void_p, c_ll, c_void_p, c_int, c_int, c_int, c_void_p])
+
+
+def _is32(t: torch.Tensor) -> int:
+    if t.dtype not in (torch.float32, torch.bfloat16):
+        raise TypeError(f"activations must be bfloat16 or float32, got {t.dtype}")
+    return int(t.dtype == torch.float32)
+
+
+def rope_frequencies(dims: int, base: float, scaling: Optional[Dict[str, Any]] = None) -> Tuple[torch.Tensor, float]:
+    """Per-pair frequencies ``f_i = base^(-2i/dims)`` (fp32, [dims/2]) and the factor applied to cos and sin.
+    ``scaling`` = {factor, original, fast, slow} blends towards ``f_i / factor`` between the pairs that make
+    ``fast`` and ``slow`` turns over ``original`` positions (YaRN), and raises the cos/sin amplitude to
+    ``0.1 ln(factor) + 1``."""
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    f = torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / dims)
+    mult = 1.0
+    if scaling:
+        factor, orig = float(scaling["factor"]), float(scaling["original"])
+
+        def pair_of(turns: float) -> float:
+            return dims * math.log(orig / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+        lo = max(math.floor(pair_of(float(scaling["fast"]))), 0)
+        hi = min(math.ceil(pair_of(float(scaling["slow"]))), dims - 1)
+        ramp = ((i - lo) / max(hi - lo, 0.001)).clamp_(0.0, 1.0)
+        f = f / factor * ramp + f * (1.0 - ramp)
+        mult = 0.1 * math.log(factor) + 1.0
+    return f.to(torch.float32), float(mult)
+
+
+def rotate_interleaved(x: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor, mult: float) -> torch.Tensor:
+    """CPU restatement of csrc/rope/rope_interleaved.cuh: x [T, ..., 2 * len(freq)] fp32."""
+    ang = positions.to(torch.float32).unsqueeze(-1) * freq
+    cos, sin = torch.cos(ang) * mult, torch.sin(ang) * mult
+    while cos.dim() < x.dim():
+        cos, sin = cos.unsqueeze(1), sin.unsqueeze(1)
+    u, v = x[..., 0::2], x[..., 1::2]
+    return torch.stack([u * cos - v * sin, v * cos + u * sin], dim=-1).flatten(-2)
+
+
+def embed_scale(tokens: torch.Tensor, table: torch.Tensor, scale: float) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``x = table[tokens] * scale`` -> (fp32 residual stream, the same in the table's type)."""
+    T, W = tokens.numel(), table.shape[1]
+    if table.is_cuda:
+        x = torch.empty(T, W, dtype=torch.float32, device=table.device)
+        xa = x if table.dtype == torch.float32 else torch.empty(T, W, dtype=table.dtype, device=table.device)
+        native.call("llmctl_embed_scale", tokens.data_ptr(), table.data_ptr(), _is32(table), float(scale), x.data_ptr(),
+                    None if xa is x else xa.data_ptr(), T, W, native.stream_ptr())
+        return x, xa
+    x = table[tokens.reshape(-1)].float() * scale
+    return x, (x if table.dtype == torch.float32 else x.to(table.dtype))
+
+
+def postnorm_residual(y: torch.Tensor, x: torch.Tensor, gain: torch.Tensor, eps: float, act_dtype: torch.dtype) -> torch.Tensor:
+    """``x += gain * y / rms(y)`` in place on the fp32 stream ``x``; returns the new stream in ``act_dtype`` (``x``
+    itself for fp32).  ``y``: [T, W] bf16 or fp32; ``gain``: one fp32 number on x's device."""
+    T, W = x.shape
+    assert x.dtype == torch.float32 and x.is_contiguous() and y.shape == x.shape and y.stride(1) == 1
+    if x.is_cuda:
+        xa = x if act_dtype == torch.float32 else torch.empty(T, W, dtype=act_dtype, device=x.device)
+        native.call("llmctl_postnorm_residual", y.data_ptr(), _is32(y), y.stride(0), x.data_ptr(),
+                    None if xa is x else xa.data_ptr(), int(act_dtype == torch.float32), gain.data_ptr(), T, W, float(eps),
+                    native.stream_ptr())
+        return xa
+    yf = y.float()
+    x += yf * (gain.float() / torch.sqrt(yf.pow(2).mean(-1, keepdim=True) + eps))
+    return x if act_dtype == torch.float32 else x.to(act_dtype)
+
+
+def scalar_rmsnorm(x: torch.Tensor, rows: Optional[torch.Tensor], gain: torch.Tensor, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """``gain * x[rows] / rms(x[rows])`` of the fp32 stream (all rows when ``rows`` is None) in ``out_dtype``."""
+    n = x.shape[0] if rows is None else rows.numel()
+    if x.is_cuda:
+        out = torch.empty(n, x.shape[1], dtype=out_dtype, device=x.device)
+        native.call("llmctl_scalar_rmsnorm", x.data_ptr(), native.ptr(rows), out.data_ptr(), int(out_dtype == torch.float32),
+                    gain.data_ptr(), n, x.shape[1], float(eps), native.stream_ptr())
+        return out
+    xs = x if rows is None else x[rows]
+    return (xs * (gain.float() / torch.sqrt(xs.pow(2).mean(-1, keepdim=True) + eps))).to(out_dtype)
+
+
+def softcap_(logits: torch.Tensor, cap: float) -> torch.Tensor:
+    """``cap * tanh(logits / cap)`` in place on fp32 logits."""
+    assert logits.dtype == torch.float32 and logits.is_contiguous()
+    if logits.is_cuda:
+        native.call("llmctl_softcap", logits.data_ptr(), logits.numel(), float(cap), native.stream_ptr())
+        return logits
+    return logits.copy_(cap * torch.tanh(logits / cap))
+
+
+def xielu_coefficients(p: torch.Tensor) -> Tuple[float, float]:
+    """(a_pos, a_neg) = (softplus(p0), 1/2 + softplus(p1)) in fp32 from the layer's two learned numbers."""
+    sp = F.softplus(p.detach().float().cpu())
+    return float(sp[0]), float(0.5 + sp[1])
+
+
+def xielu(z: torch.Tensor, a_pos: float, a_neg: float) -> torch.Tensor:
+    """z > 0: a_pos z^2 + z/2;  z <= 0: a_neg (exp(z) - 1 - z) + z/2."""
+    if z.is_cuda:
+        z = z.contiguous()
+        out = torch.empty_like(z)
+        native.call("llmctl_xielu", z.data_ptr(), out.data_ptr(), _is32(z), z.numel(), a_pos, a_neg, native.stream_ptr())
+        return out
+    v = z.float()
+    return torch.where(v > 0, a_pos * v * v + 0.5 * v, a_neg * (torch.expm1(v.clamp(max=0.0)) - v) + 0.5 * v).to(z.dtype)
+
+
+def gated_silu(gate_up: torch.Tensor) -> torch.Tensor:
+    """``silu(gate) * up`` of a packed [rows, 2F] activation (gate first), bf16 or fp32."""
+    rows, F2 = gate_up.shape
+    if gate_up.is_cuda:
+        assert gate_up.stride(1) == 1
+        out = torch.empty(rows, F2 // 2, dtype=gate_up.dtype, device=gate_up.device)
+        native.call("llmctl_gated_silu", gate_up.data_ptr(), gate_up.stride(0), out.data_ptr(), _is32(gate_up), rows, F2 // 2,
+                    native.stream_ptr())
+        return out
+    g, u = gate_up.float().chunk(2, dim=-1)
+    return (F.silu(g) * u).to(gate_up.dtype)

@@ -1,0 +1,90 @@
+"""Latent (low-rank joint key/value) attention over a paged cache — csrc/attention/latent_attention.cu.
+
+The cache row of a token is ``[c | kr]``: the normed latent (R numbers) and the rotated key part shared by all heads
+(dr numbers).  ``latent_kv_write`` norms the query latent, norms + rotates + appends the key/value side;
+``latent_attention`` is multi-query attention of absorbed queries against those rows for a ragged batch (portions
+of prompts next to single decoded tokens).  CPU tensors run a PyTorch restatement.
+
+Reference: none — the reference has no attention code (reference llmctl/serve/server.py:199-204)."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import native
+from .elementwise import _is32, rotate_interleaved
+
+c_void_p, c_int, c_ll, c_float = native.c_void_p, native.c_int, native.c_ll, native.c_float
+native.register_signature("llmctl_latent_kv_write", [c_void_p, c_ll, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                      c_void_p, c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_void_p])
+native.register_signature("llmctl_latent_attention", [c_void_p, c_void_p, c_ll, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p,
+                                                       c_int, c_int, c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_int,
+                                                       c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
+native._KERNELS_PER_CALL["llmctl_latent_attention"] = 1
+
+ROWS_PER_TILE = 16          # query rows (token, head) a CTA owns; tiles are built by the engine with this limit
+
+
+def latent_kv_write(d: torch.Tensor, Q: int, R: int, dr: int, wq: torch.Tensor, wkv: Optional[torch.Tensor],
+                    cache: Optional[torch.Tensor], slots: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor,
+                    mult: float, eps: float) -> torch.Tensor:
+    """d: [T, Q + R + dr] = raw [query latent | key/value latent | key rope part] (R = dr = 0 for a layer without a
+    cache of its own).  Returns the normed query latent [T, Q]; writes ``[norm(c) * wkv | rotate(kr)]`` into
+    ``cache`` ([blocks, block_size, R + dr]) at ``slots`` (int64 [T], negative = skip)."""
+    T = d.shape[0]
+    if d.is_cuda:
+        assert d.stride(1) == 1
+        cq = torch.empty(T, Q, dtype=d.dtype, device=d.device)
+        native.call("llmctl_latent_kv_write", d.data_ptr(), d.stride(0), Q, R, dr, wq.data_ptr(), native.ptr(wkv), cq.data_ptr(),
+                    native.ptr(cache), slots.data_ptr(), positions.data_ptr(), freq.data_ptr(), float(mult), float(eps), T,
+                    _is32(d), native.stream_ptr())
+        return cq
+    f = d.float()
+
+    def norm(v, w):
+        return v / torch.sqrt(v.pow(2).mean(-1, keepdim=True) + eps) * w.float()
+    cq = norm(f[:, :Q], wq).to(d.dtype)
+    if R:
+        row = torch.cat([norm(f[:, Q:Q + R], wkv), rotate_interleaved(f[:, Q + R:Q + R + dr], positions, freq, mult)], dim=-1)
+        ok = slots >= 0
+        cache.view(-1, R + dr)[slots[ok]] = row[ok].to(cache.dtype)
+    return cq
+
+
+def latent_attention(ql: torch.Tensor, q: torch.Tensor, dn: int, cache: torch.Tensor, block_tables: torch.Tensor,
+                     tiles: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor, mult: float, scale: float,
+                     heads_per_tile: int, max_context: int, splits: int = 1) -> torch.Tensor:
+    """ql: fp32 [T, H, R] absorbed queries; q: [T, H * (dn + dr)] raw queries (the rope part of each head is rotated
+    here); tiles: int32 [n, 4] = (first token row, tokens, block-table row, 0) with tokens * heads_per_tile <=
+    ROWS_PER_TILE, all tokens of a tile in one sequence with growing positions.  Returns [T, H, R] in q's type:
+    softmax(scale * (ql . c + rot(qr) . kr)) c over cache positions 0..position of each token."""
+    T, H, R = ql.shape
+    D = cache.shape[-1]
+    dr = D - R
+    block_size = cache.shape[1]
+    if q.is_cuda:
+        assert ql.dtype == torch.float32 and ql.is_contiguous() and q.stride(1) == 1 and cache.is_contiguous()
+        out = torch.empty(T, H, R, dtype=q.dtype, device=q.device)
+        splits = max(1, int(splits))
+        per = (max_context + splits - 1) // splits
+        per = max(32, (per + 31) // 32 * 32)
+        partial = torch.empty(T * H * splits * (R + 2), dtype=torch.float32, device=q.device) if splits > 1 else None
+        native.call("llmctl_latent_attention", ql.data_ptr(), q.data_ptr(), q.stride(0), dn, cache.data_ptr(),
+                    block_tables.data_ptr(), block_tables.shape[1], block_size, tiles.data_ptr(), tiles.shape[0], T,
+                    positions.data_ptr(), freq.data_ptr(), float(mult), float(scale), H, R, dr, heads_per_tile, splits, per,
+                    out.data_ptr(), native.ptr(partial), _is32(q), native.stream_ptr())
+        return out
+    out = torch.zeros(T, H, R, dtype=torch.float32)
+    rows = cache.view(-1, D).float()
+    qh = q.float().view(T, H, dn + dr)
+    for t0, n, seq, _ in tiles.tolist():
+        bt = block_tables[seq].long()
+        for t in range(t0, t0 + n):
+            p = int(positions[t])
+            j = torch.arange(p + 1)
+            kv = rows[bt[j // block_size] * block_size + j % block_size]          # [p + 1, D]
+            qr = rotate_interleaved(qh[t, :, dn:], positions[t:t + 1].expand(H), freq, mult)
+            s = (ql[t] @ kv[:, :R].t() + qr @ kv[:, R:].t()) * scale
+            out[t] = torch.softmax(s, -1) @ kv[:, :R]
+    return out.to(q.dtype)

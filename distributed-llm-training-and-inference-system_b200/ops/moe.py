@@ -1,0 +1,98 @@
+"""Mixture-of-experts feed-forward — csrc/moe/moe.cu: routing (sigmoid or softmax scores, top-k, optional
+renormalisation), device-side token permutation into per-expert segments, grouped expert GEMMs and the combine, with
+the routing weight applied to the expert's input or to its output.  No host synchronisation on CUDA.  CPU tensors run
+a PyTorch restatement.
+
+Reference: none — the reference has no model code."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import native
+from .elementwise import _is32, gated_silu
+
+c_void_p, c_int, c_ll, c_float = native.c_void_p, native.c_int, native.c_ll, native.c_float
+native.register_signature("llmctl_moe_route", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
+native.register_signature("llmctl_moe_plan", [c_void_p, c_int, c_void_p, c_int, c_void_p])
+native.register_signature("llmctl_moe_permute", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                                                  c_int, c_int, c_int, c_void_p])
+native.register_signature("llmctl_grouped_gemm", [c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_int, c_int, c_void_p, c_int, c_int,
+                                                   c_int, c_void_p])
+native.register_signature("llmctl_moe_combine", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                                  c_int, c_int, c_void_p])
+TILE_ROWS = 64      # row tile of the grouped GEMM (llmctl_moe_tile_rows)
+
+
+def route(x: torch.Tensor, w_router: torch.Tensor, top: int, w_gate: Optional[torch.Tensor] = None, softmax: bool = False,
+          renormalise: bool = False):
+    """x: fp32 [T, W].  Returns (ids int32 [T, top], weights fp32 [T, top], gate fp32 [T] or None, counts int32 [E])."""
+    T, W = x.shape
+    E = w_router.shape[0]
+    if x.is_cuda:
+        ids = torch.empty(T, top, dtype=torch.int32, device=x.device)
+        wts = torch.empty(T, top, dtype=torch.float32, device=x.device)
+        gate = torch.empty(T, dtype=torch.float32, device=x.device) if w_gate is not None else None
+        counts = torch.empty(E, dtype=torch.int32, device=x.device)
+        native.call("llmctl_moe_route", x.data_ptr(), w_router.data_ptr(), native.ptr(w_gate), _is32(w_router), T, W, E, top,
+                    int(softmax), int(renormalise), ids.data_ptr(), wts.data_ptr(), native.ptr(gate), counts.data_ptr(),
+                    native.stream_ptr())
+        return ids, wts, gate, counts
+    z = x @ w_router.float().t()
+    s = torch.softmax(z, -1) if softmax else torch.sigmoid(z)
+    wts, ids = torch.topk(s, top, dim=-1)
+    if renormalise:
+        wts = wts / wts.sum(-1, keepdim=True)
+    gate = torch.sigmoid(x @ w_gate.float().reshape(-1)) if w_gate is not None else None
+    return ids.to(torch.int32), wts, gate, torch.bincount(ids.reshape(-1), minlength=E).to(torch.int32)
+
+
+def moe_ffn(x: torch.Tensor, act_dtype: torch.dtype, w_router: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor,
+            top: int, *, scale_input: bool, shared_out: Optional[torch.Tensor] = None, w_shared_gate: Optional[torch.Tensor] = None,
+            softmax: bool = False, renormalise: bool = False) -> torch.Tensor:
+    """x: fp32 [T, W] stream; w_gate_up: [E, 2F, W] (gate rows first); w_down: [E, W, F]; ``shared_out``: [T, W] output
+    of a shared expert that runs for every token, multiplied by sigmoid(w_shared_gate . x) when that is given.
+    Returns fp32 [T, W] = sum over the chosen experts (+ shared).  ``scale_input``: the routing weight multiplies the
+    expert's input (expert(w x)); otherwise its output (w expert(x))."""
+    T, W = x.shape
+    E, F2, _ = w_gate_up.shape
+    ids, wts, gate, counts = route(x, w_router, top, w_shared_gate, softmax, renormalise)
+    if x.is_cuda:
+        is32 = int(act_dtype == torch.float32)
+        pairs = T * top
+        max_tiles = (pairs + TILE_ROWS - 1) // TILE_ROWS + E
+        meta = torch.empty(2 * E + 2 + max_tiles, dtype=torch.int32, device=x.device)
+        pair_row = torch.empty(pairs, dtype=torch.int32, device=x.device)
+        xs = torch.empty(max_tiles * TILE_ROWS, W, dtype=act_dtype, device=x.device)
+        st = native.stream_ptr()
+        native.call("llmctl_moe_plan", counts.data_ptr(), E, meta.data_ptr(), max_tiles, st)
+        native.call("llmctl_moe_permute", x.data_ptr(), W, ids.data_ptr(), wts.data_ptr(), int(scale_input), meta.data_ptr(), E,
+                    pair_row.data_ptr(), xs.data_ptr(), is32, T, top, st)
+        gu = torch.empty(max_tiles * TILE_ROWS, F2, dtype=act_dtype, device=x.device)
+        native.call("llmctl_grouped_gemm", xs.data_ptr(), W, w_gate_up.data_ptr(), gu.data_ptr(), F2, F2, W, meta.data_ptr(), E,
+                    max_tiles, is32, st)
+        act = gated_silu(gu)
+        eo = torch.empty(max_tiles * TILE_ROWS, W, dtype=act_dtype, device=x.device)
+        native.call("llmctl_grouped_gemm", act.data_ptr(), F2 // 2, w_down.data_ptr(), eo.data_ptr(), W, W, F2 // 2, meta.data_ptr(),
+                    E, max_tiles, is32, st)
+        y = torch.empty(T, W, dtype=torch.float32, device=x.device)
+        native.call("llmctl_moe_combine", eo.data_ptr(), W, pair_row.data_ptr(), wts.data_ptr(), top, int(not scale_input),
+                    native.ptr(shared_out), native.ptr(gate), y.data_ptr(), T, is32, st)
+        return y
+    y = torch.zeros(T, W, dtype=torch.float32)
+    for k in range(top):
+        for e in range(E):
+            sel = (ids[:, k] == e).nonzero().reshape(-1)
+            if sel.numel() == 0:
+                continue
+            w = wts[sel, k].unsqueeze(-1)
+            xin = (x[sel] * w if scale_input else x[sel]).to(act_dtype)
+            h = gated_silu(F.linear(xin, w_gate_up[e]))
+            o = F.linear(h, w_down[e]).float()
+            y[sel] += o if scale_input else w * o
+    if shared_out is not None:
+        y += shared_out.float() * (gate.unsqueeze(-1) if gate is not None else 1.0)
+    return y

@@ -1,5 +1,11 @@
 """Inference engine: paged KV cache, continuous batching, native decode kernels.
 
+Two kinds of models are served.  The GPT/LLaMA family (below) prefills sequence by sequence and decodes as a batch.
+Models that declare ``ragged = True`` (``models/nafazen.py``) run every step as ONE ragged batch — whole prompts,
+portions of prompts and single decoded tokens side by side (``serve/ragged.py``) — against caches they lay out
+themselves (``allocate_caches``); ``forward_portions`` is that step function, used by ``step()`` and by trace replay
+(``serve/replay.py``) alike.
+
 One ``step()`` = one scheduler step: newly admitted sequences are prefilled (dense causal attention over the
 prompt, K/V scattered into their cache blocks — kernel K13), all running sequences then decode one token
 together (packed qkv GEMM, RoPE at each sequence's own position, K13 append, K12 paged attention over the
@@ -28,37 +34,45 @@ from ..models.gpt import GPTModel, build_model
 from ..ops import functional as ops
 from ..ops import serving as sops
 from .native_host import DECODE, PREFILL, BatchScheduler, KVBlockManager
+from .ragged import Portion, RaggedBatch
 from .tokenizer import load_tokenizer
 
 
-def load_model_for_inference(artifact: str | Path, device: Optional[str] = None, dtype: Optional[torch.dtype] = None
+def load_model_for_inference(artifact, device: Optional[str] = None, dtype: Optional[torch.dtype] = None
                              ) -> Tuple[GPTModel, ModelConfig, object, torch.device]:
     """Load a checkpoint / exported artifact directory (``model_config.json`` + ``model.safetensors`` or TP/PP
-    shards), or build a random-init preset when ``artifact`` names one (benchmarks)."""
+    shards, or the ``config.json`` + ``model.safetensors`` of a registered architecture), or build a random-init model
+    when ``artifact`` names a preset or is a configuration object / dictionary (benchmarks, tests)."""
     from ..io.export import consolidate_to_state_dict, shard_state_dict_for
+    from ..models import registry
     st = get_state()
     if device in (None, "auto"):
         dev = st.device if st.world_size > 1 else torch.device("cuda" if torch.cuda.is_available() else "cpu")
     else:
         dev = torch.device(device)
     dtype = dtype or (torch.bfloat16 if dev.type == "cuda" else torch.float32)
-    p = Path(str(artifact))
-    if p.is_dir():
+    is_path = isinstance(artifact, (str, Path))
+    p = Path(str(artifact)) if is_path else None
+    if p is not None and p.is_dir():
         from ..io.export import load_pretrained_state_dict
-        mcfg = resolve_model(p)                                  # model_config.json, or an HF config.json
+        mcfg = resolve_model(p)                                  # model_config.json, an HF config.json, or a registered design
         model = build_model(mcfg, dtype=dtype, device=dev)
-        full = load_pretrained_state_dict(p)                     # our names or HF LlamaForCausalLM names
-        local = shard_state_dict_for(full, model)
-        with torch.no_grad():
-            for k, prm in model.named_parameters():
-                prm.copy_(local[k].to(dev, dtype))
+        arch = registry.architecture_of(mcfg)
+        if arch is not None and arch.load_weights is not None:
+            arch.load_weights(model, p)
+        else:
+            full = load_pretrained_state_dict(p)                 # our names or HF LlamaForCausalLM names
+            local = shard_state_dict_for(full, model)
+            with torch.no_grad():
+                for k, prm in model.named_parameters():
+                    prm.copy_(local[k].to(dev, dtype))
     else:
-        mcfg = resolve_model(str(artifact))
+        mcfg = resolve_model(str(artifact) if is_path else artifact)
         model = build_model(mcfg, dtype=dtype, device=dev)
     model.eval()
     for prm in model.parameters():
         prm.requires_grad_(False)
-    tok = load_tokenizer(str(artifact), mcfg.vocab_size)
+    tok = load_tokenizer(str(artifact) if is_path else None, mcfg.vocab_size)
     return model, mcfg, tok, dev
 
 
@@ -206,17 +220,23 @@ class InferenceEngine:
     def __init__(self, artifact: str | Path, *, max_batch_size: int = 8, max_batch_tokens: int = 8192,
                  scheduler: str = "dynamic", device: Optional[str] = None, kv_block_size: int = 16,
                  kv_memory_fraction: float = 0.5, num_kv_blocks: Optional[int] = None, seed: int = 0,
-                 cuda_graphs: Optional[bool] = None, fused_tp_decode: Optional[bool] = None):
-        self.model, self.cfg, self.tokenizer, self.device = load_model_for_inference(artifact, device)
+                 cuda_graphs: Optional[bool] = None, fused_tp_decode: Optional[bool] = None,
+                 dtype: Optional[torch.dtype] = None, kv_watermark: float = 0.01):
+        self.model, self.cfg, self.tokenizer, self.device = load_model_for_inference(artifact, device, dtype)
         self.st = get_state()
         self.lockstep = False       # True under serve/lockstep.py: cancellations take effect on all TP ranks at once
         m = self.model
-        self.heads_local = m.blocks[0].attn.heads_local
-        self.head_dim = self.cfg.head_dim
+        self.ragged = bool(getattr(m, "ragged", False))      # one ragged batch per step against the model's own caches
+        if not self.ragged:
+            self.heads_local = m.blocks[0].attn.heads_local
+            self.head_dim = self.cfg.head_dim
         self.block_size = kv_block_size
-        self.dtype = next(m.parameters()).dtype
+        self.dtype = m.dtype if self.ragged else next(m.parameters()).dtype
         if num_kv_blocks is None:
-            per_block = 2 * len(m.blocks) * kv_block_size * self.heads_local * self.head_dim * self.dtype.itemsize
+            if self.ragged:
+                per_block = max(m.cache_bytes_per_block(kv_block_size), 1)
+            else:
+                per_block = 2 * len(m.blocks) * kv_block_size * self.heads_local * self.head_dim * self.dtype.itemsize
             if self.device.type == "cuda":
                 free, _ = torch.cuda.mem_get_info(self.device)
                 num_kv_blocks = int(free * kv_memory_fraction // per_block)
@@ -224,7 +244,7 @@ class InferenceEngine:
                 num_kv_blocks = 512
             want = (max_batch_tokens + kv_block_size - 1) // kv_block_size + max_batch_size
             num_kv_blocks = max(min(num_kv_blocks, 8 * want), want)
-        self.kv = KVBlockManager(num_kv_blocks, kv_block_size)
+        self.kv = KVBlockManager(num_kv_blocks, kv_block_size, kv_watermark)
         # a scheduler plugin (user-guide contract: ``schedule(requests) -> ordered requests``) decides the ORDER in
         # which waiting requests are handed to the native continuous-batching core; budgets, KV accounting and
         # preemption stay in the C++ scheduler
@@ -239,9 +259,13 @@ class InferenceEngine:
             self._plugin_sched = factory() if callable(factory) else factory
             scheduler = "dynamic"
         self.sched = BatchScheduler(max_batch_size, max_batch_tokens, scheduler, self.kv)
-        shape = (num_kv_blocks, kv_block_size, self.heads_local, self.head_dim)
-        self.k_caches = [torch.zeros(shape, dtype=self.dtype, device=self.device) for _ in m.blocks]
-        self.v_caches = [torch.zeros(shape, dtype=self.dtype, device=self.device) for _ in m.blocks]
+        if self.ragged:
+            self.caches = m.allocate_caches(num_kv_blocks, kv_block_size, self.device)
+            self.k_caches, self.v_caches = [], []
+        else:
+            shape = (num_kv_blocks, kv_block_size, self.heads_local, self.head_dim)
+            self.k_caches = [torch.zeros(shape, dtype=self.dtype, device=self.device) for _ in m.blocks]
+            self.v_caches = [torch.zeros(shape, dtype=self.dtype, device=self.device) for _ in m.blocks]
         self.seqs: Dict[int, Sequence] = {}
         self._next_id = 1
         self._lock = threading.Lock()
@@ -261,7 +285,7 @@ class InferenceEngine:
         self._ar: Optional[_DecodeAllReduce] = None
         if fused_tp_decode is None:
             fused_tp_decode = True
-        if (fused_tp_decode and self.st.tp > 1 and self.device.type == "cuda" and self.cfg.norm == "rmsnorm"
+        if (fused_tp_decode and not self.ragged and self.st.tp > 1 and self.device.type == "cuda" and self.cfg.norm == "rmsnorm"
                 and not self.st.sequence_parallel):
             from ..comms import symm
             from ..ops import native
@@ -310,6 +334,48 @@ class InferenceEngine:
                 if seq is not None:
                     seq.finished, seq.finish_reason = True, "error"
                     seq.done_event.set()
+
+    # ---- ragged models: one batch per step ------------------------------------------------------------
+    @torch.no_grad()
+    def forward_portions(self, portions: List[Portion], layer_trace: Optional[list] = None) -> torch.Tensor:
+        """The step function of ragged models: run the given portions (each sequence's next tokens; its cache blocks
+        must already cover them) as one batch; returns fp32 logits [total wanted positions, vocab]."""
+        assert self.ragged, "forward_portions serves models that declare ragged = True"
+        batch = RaggedBatch(portions, self.block_size, self.device)
+        self.stats["batch_tokens"] = self.stats.get("batch_tokens", 0) + batch.num_tokens
+        self.stats["h2d_bytes"] = self.stats.get("h2d_bytes", 0) + batch.nbytes
+        return self.model.forward_ragged(batch, self.caches, layer_trace)
+
+    def portion(self, seq_id: int, tokens: List[int], start: int, want: List[int]) -> Portion:
+        return Portion(seq_id, tokens, start, want, self.kv.block_table(seq_id))
+
+    def _step_ragged(self, plan) -> List[Sequence]:
+        """Prefills (whole prompt, or prompt + generated tokens after a preemption) and decodes of one scheduler step
+        as a single batch; every sequence samples from the logits of its last token."""
+        finished: List[Sequence] = []
+        seqs, portions = [], []
+        for r, ph, _ in plan:
+            s = self.seqs[r]
+            ids = s.all_ids
+            if ph == PREFILL:
+                portions.append(self.portion(r, ids, 0, [len(ids) - 1]))
+                self.stats["prefill_tokens"] += len(ids)
+            else:
+                portions.append(self.portion(r, ids[-1:], len(ids) - 1, [0]))
+                self.stats["decode_tokens"] += 1
+            seqs.append(s)
+        t0 = time.perf_counter()
+        toks = self._sample(self.forward_portions(portions), seqs)
+        dt = time.perf_counter() - t0
+        if any(ph == PREFILL for _, ph, _ in plan):
+            self.stats["prefill_time_s"] += dt
+        else:
+            self.stats["decode_time_s"] += dt
+            self.stats["decode_steps"] += 1
+        for s, tok in zip(seqs, toks):
+            self._emit(s, tok, finished)      # the logits exist already, so a sequence evicted by another's growth
+        self.stats["preemptions"] += len(self.sched.pop_preempted())     # still emits its token (counted for re-prefill)
+        return finished
 
     # ---- model pieces ----------------------------------------------------------------------------------
     def _slots(self, rid: int, start: int, count: int) -> torch.Tensor:
@@ -483,6 +549,8 @@ class InferenceEngine:
         if not plan:
             return []
         self.stats["steps"] += 1
+        if self.ragged:
+            return self._step_ragged(plan)
         finished: List[Sequence] = []
         decode = [self.seqs[r] for r, ph, _ in plan if ph == DECODE]
         # A token's KV growth may evict other sequences of this very plan (their blocks are gone).  Evicted sequences

@@ -1,0 +1,95 @@
+"""Ragged batch of one engine step: portions of prompts next to single decoded tokens, over the paged cache.
+
+The host builds the whole description (tokens, positions, cache slots, block tables, attention query tiles, rows
+whose logits are wanted) in one pinned int32 staging buffer; one copy takes it to the device.  Models that declare
+``ragged = True`` consume it in ``forward_ragged`` (``models/nafazen.py``).
+
+Reference: the reference right-pads a batch and recomputes whole sequences (reference llmctl/serve/server.py:171-204)."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Sequence as Seq, Tuple
+
+import numpy as np
+import torch
+
+from ..ops.latent_attention import ROWS_PER_TILE
+
+
+@dataclass
+class Portion:
+    """The next ``len(tokens)`` tokens of one sequence, which already holds ``start`` tokens in the cache; ``want`` lists
+    the offsets within ``tokens`` whose logits are asked for."""
+    seq_id: int
+    tokens: Seq[int]
+    start: int
+    want: Seq[int]
+    block_table: Seq[int]
+
+
+class RaggedBatch:
+    def __init__(self, portions: List[Portion], block_size: int, device: torch.device, sm_count: int = 148):
+        T = sum(len(p.tokens) for p in portions)
+        B = len(portions)
+        assert T > 0
+        self.decode_only = all(len(p.tokens) == 1 for p in portions)
+        self.tokens_per_tile = 1 if self.decode_only else ROWS_PER_TILE
+        self.max_context = max(p.start + len(p.tokens) for p in portions)
+        max_blocks = max(len(p.block_table) for p in portions)
+        n_out = sum(len(p.want) for p in portions)
+        ntiles = sum((len(p.tokens) + self.tokens_per_tile - 1) // self.tokens_per_tile for p in portions)
+        # int32 words: tokens(2T) | slots(2T) | out_rows(2 n_out) | positions(T) | tiles(4 ntiles) | block tables(B max_blocks)
+        sizes = [2 * T, 2 * T, 2 * n_out, T, 4 * ntiles, B * max_blocks]
+        offs = np.concatenate([[0], np.cumsum(sizes)])
+        host = torch.zeros(int(offs[-1]), dtype=torch.int32, pin_memory=device.type == "cuda")
+        a = host.numpy()
+        tokens = a[offs[0]:offs[1]].view(np.int64)
+        slots = a[offs[1]:offs[2]].view(np.int64)
+        out_rows = a[offs[2]:offs[3]].view(np.int64)
+        positions = a[offs[3]:offs[4]]
+        tiles = a[offs[4]:offs[5]].reshape(ntiles, 4)
+        tables = a[offs[5]:offs[6]].reshape(B, max_blocks)
+        t = o = ti = 0
+        for b, p in enumerate(portions):
+            n = len(p.tokens)
+            bt = np.asarray(p.block_table, dtype=np.int64)
+            pos = np.arange(p.start, p.start + n)
+            assert len(bt) * block_size >= p.start + n, "the sequence owns too few cache blocks for this portion"
+            tokens[t:t + n] = np.asarray(p.tokens, dtype=np.int64)
+            positions[t:t + n] = pos
+            slots[t:t + n] = bt[pos // block_size] * block_size + pos % block_size
+            tables[b, :len(bt)] = bt
+            for w in p.want:
+                assert 0 <= w < n
+                out_rows[o] = t + w
+                o += 1
+            for s in range(0, n, self.tokens_per_tile):
+                tiles[ti] = (t + s, min(self.tokens_per_tile, n - s), b, 0)
+                ti += 1
+            t += n
+        dev = host.to(device, non_blocking=True) if device.type == "cuda" else host
+        self.nbytes = host.numel() * 4
+        self.num_tokens, self.num_out, self.num_tiles = T, n_out, ntiles
+        self.tokens = dev[offs[0]:offs[1]].view(torch.int64)
+        self.slots = dev[offs[1]:offs[2]].view(torch.int64)
+        self.out_rows = dev[offs[2]:offs[3]].view(torch.int64)
+        self.positions = dev[offs[3]:offs[4]]
+        self._tiles = dev[offs[4]:offs[5]].view(ntiles, 4)
+        self.block_tables = dev[offs[5]:offs[6]].view(B, max_blocks)
+        self._sms = sm_count
+        self._host = host      # keeps the pinned buffer alive until the copy has run
+
+    # ---- attention tiling -----------------------------------------------------------------------------------
+    def tiles(self, heads: int) -> torch.Tensor:
+        return self._tiles
+
+    def heads_per_tile(self, heads: int) -> int:
+        """A tile holds ROWS_PER_TILE (token, head) rows: 16 tokens x 1 head in a batch with prompt portions, 1 token x up
+        to 16 heads when every sequence decodes."""
+        return min(heads, ROWS_PER_TILE) if self.decode_only else 1
+
+    def attention_splits(self, heads: int) -> int:
+        """Split the keys of long contexts over CTAs when the tiles alone would leave most SMs idle."""
+        hpt = self.heads_per_tile(heads)
+        ctas = self.num_tiles * ((heads + hpt - 1) // hpt)
+        return int(max(1, min(2 * self._sms // max(ctas, 1), self.max_context // 128)))

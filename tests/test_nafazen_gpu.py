@@ -1,0 +1,163 @@
+"""Nafazen on a B200: every new kernel against the PyTorch restatement of the same op on the CPU (bf16 and fp32),
+then the served model against the plain oracle: whole prompts, decoding through the cache, portions and mixed
+batches, in fp32 (tight) and bf16."""
+import copy
+
+import pytest
+import torch
+
+import nafazen_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dt):
+    return 2e-5 if dt == torch.float32 else 2e-2
+
+
+def close(a, b, dt, scale=1.0):
+    err = (a.float().cpu() - b.float().cpu()).abs().max().item()
+    assert err <= tol(dt) * scale, f"max err {err}"
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+def test_elementwise_kernels(cuda_device, dt):
+    from llmctl_b200.ops import elementwise as E
+    torch.manual_seed(0)
+    T, W = 37, 72
+    table = torch.randn(50, W).to(dt)
+    toks = torch.randint(0, 50, (T,))
+    x_c, xa_c = E.embed_scale(toks, table, 0.7)
+    x_g, xa_g = E.embed_scale(toks.cuda(), table.cuda(), 0.7)
+    close(x_g, x_c, torch.float32)
+    close(xa_g, xa_c, dt)
+    y = torch.randn(T, W).to(dt)
+    g = torch.tensor(1.3)
+    h_c = E.postnorm_residual(y, x_c, g, 1e-5, dt)
+    h_g = E.postnorm_residual(y.cuda(), x_g, g.cuda(), 1e-5, dt)
+    close(x_g, x_c, torch.float32)
+    close(h_g, h_c, dt, 4)
+    yf = torch.randn(T, W)
+    E.postnorm_residual(yf, x_c, g, 1e-5, dt)
+    E.postnorm_residual(yf.cuda(), x_g, g.cuda(), 1e-5, dt)
+    close(x_g, x_c, torch.float32)
+    rows = torch.tensor([3, 0, 36])
+    close(E.scalar_rmsnorm(x_g, rows.cuda(), g.cuda(), 1e-5, dt), E.scalar_rmsnorm(x_c, rows, g, 1e-5, dt), dt, 4)
+    z = (torch.randn(T, W) * 3).to(dt)
+    close(E.xielu(z.cuda(), 0.8, 1.1), E.xielu(z, 0.8, 1.1), dt, 16)
+    gu = torch.randn(T, 2 * W).to(dt)
+    close(E.gated_silu(gu.cuda()), E.gated_silu(gu), dt, 4)
+    lg = torch.randn(T, W) * 40
+    close(E.softcap_(lg.clone().cuda(), 30.0), E.softcap_(lg.clone(), 30.0), torch.float32, 30)
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("H,dn,dr,R,Q,bs", [(3, 8, 4, 24, 20, 16), (5, 16, 8, 160, 40, 64), (17, 4, 2, 40, 8, 8)])
+def test_latent_attention_kernels(cuda_device, dt, H, dn, dr, R, Q, bs):
+    from llmctl_b200.ops import latent_attention as L
+    from llmctl_b200.ops.elementwise import rope_frequencies
+    from llmctl_b200.serve.ragged import Portion, RaggedBatch
+    torch.manual_seed(1)
+    nb = 24
+    freq, mult = rope_frequencies(dr, 10000.0, {"factor": 4.0, "original": 32, "fast": 8.0, "slow": 1.0})
+    cache = torch.zeros(nb, bs, R + dr, dtype=dt)
+    perm = torch.randperm(nb).tolist()
+    lens = [3 * bs + 5, 1, bs, 2 * bs - 1]
+    tables, used = [], 0
+    for n in lens:
+        k = (n + bs - 1) // bs
+        tables.append(perm[used:used + k])
+        used += k
+    wq, wkv = torch.rand(Q).add(0.5).to(dt), torch.rand(R).add(0.5).to(dt)
+    cache_g = cache.cuda()
+    # two rounds: whole prompts minus a tail, then (a) decode-only batch and (b) a mixed batch
+    for rnd, cut in enumerate([[n - min(n - 1, 3) if n > 1 else 1 for n in lens], lens]):
+        portions = []
+        for i, n in enumerate(lens):
+            start = 0 if rnd == 0 else [m - min(m - 1, 3) if m > 1 else 1 for m in lens][i]
+            cnt = cut[i] - start
+            if cnt > 0:
+                portions.append(Portion(i, [0] * cnt, start, [], tables[i]))
+        for dev, cch in (("cpu", cache), ("cuda", cache_g)):
+            b = RaggedBatch(portions, bs, torch.device(dev))
+            T = b.num_tokens
+            g = torch.Generator().manual_seed(100 + rnd)
+            d = torch.randn(T, Q + R + dr, generator=g).to(dt).to(dev)
+            q = torch.randn(T, H * (dn + dr), generator=g).to(dt).to(dev)
+            ql = torch.randn(T, H, R, generator=g).to(dev)
+            cq = L.latent_kv_write(d, Q, R, dr, wq.to(dev), wkv.to(dev), cch, b.slots, b.positions, freq.to(dev), mult, 1e-5)
+            out = L.latent_attention(ql, q, dn, cch, b.block_tables, b.tiles(H), b.positions, freq.to(dev), mult, 0.3,
+                                     b.heads_per_tile(H), b.max_context, b.attention_splits(H) if rnd == 0 else 2)
+            if dev == "cpu":
+                ref = (cq, out)
+        close(cq, ref[0], dt, 4)
+        close(out, ref[1], dt, 4)
+    close(cache_g, cache, dt, 4)
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("T,E,top,scale_input", [(70, 5, 2, True), (3, 8, 1, True), (200, 3, 3, False)])
+def test_moe_kernels(cuda_device, dt, T, E, top, scale_input):
+    from llmctl_b200.ops import moe as M
+    torch.manual_seed(2)
+    W, F = 40, 24
+    x = torch.randn(T, W)
+    wr = (torch.randn(E, W) * 0.5).to(dt)
+    wgu = (torch.randn(E, 2 * F, W) / W ** 0.5).to(dt)
+    wd = (torch.randn(E, W, F) / F ** 0.5).to(dt)
+    sg = torch.randn(W).to(dt)
+    shared = torch.randn(T, W).to(dt)
+    ids_c, w_c, g_c, cnt_c = M.route(x, wr, top, sg)
+    ids_g, w_g, g_g, cnt_g = M.route(x.cuda(), wr.cuda(), top, sg.cuda())
+    assert torch.equal(ids_g.cpu(), ids_c) and torch.equal(cnt_g.cpu(), cnt_c)
+    close(w_g, w_c, torch.float32)
+    close(g_g, g_c, torch.float32)
+    y_c = M.moe_ffn(x, dt, wr, wgu, wd, top, scale_input=scale_input, shared_out=shared, w_shared_gate=sg)
+    y_g = M.moe_ffn(x.cuda(), dt, wr.cuda(), wgu.cuda(), wd.cuda(), top, scale_input=scale_input, shared_out=shared.cuda(),
+                    w_shared_gate=sg.cuda())
+    close(y_g, y_c, dt, 8)
+
+
+def _engine(cfg, weights, dt, device, blocks=12, bs=16):
+    from llmctl_b200.serve.engine import InferenceEngine
+    eng = InferenceEngine(cfg, max_batch_size=4, max_batch_tokens=blocks * bs, device=device, kv_block_size=bs, num_kv_blocks=blocks,
+                          dtype=dt, kv_watermark=0.0, cuda_graphs=False)
+    eng.model.load_state(weights)
+    return eng
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+def test_model_matches_oracle_on_gpu(cuda_device, dt):
+    """Whole prompt, then portions + token-by-token decoding of the same prompt through the paged cache, and a mixed
+    batch of two requests, all against the oracle's logits."""
+    from llmctl_b200.models.nafazen import example_config
+    cfg = example_config()
+    w = oracle.random_weights(cfg, seed=3)
+    torch.manual_seed(5)
+    toks = torch.randint(0, cfg["vocab"], (75,)).tolist()
+    ref = oracle.forward(cfg, w, toks, exact=True)
+    limit = 3e-4 if dt == torch.float32 else 0.25
+    eng = _engine(copy.deepcopy(cfg), w, dt, "cuda")
+    assert eng.kv.allocate(1, len(toks))
+    got = eng.forward_portions([eng.portion(1, toks, 0, list(range(len(toks))))]).cpu()
+    assert (got - ref).abs().max().item() < limit
+    eng.kv.free(1)
+    # portions of 16 + 2 + 30, then decode; a second request rides along in the same batches
+    other = toks[10:40]
+    ref2 = oracle.forward(cfg, w, other, exact=True)
+    cuts, at, at2 = [16, 2, 30] + [1] * 27, 0, 0
+    for c in cuts:
+        ps = []
+        assert eng.kv.allocate(2, at + c)
+        ps.append(eng.portion(2, toks[at:at + c], at, list(range(c))))
+        c2 = min(3, len(other) - at2)
+        if c2 > 0:
+            assert eng.kv.allocate(3, at2 + c2)
+            ps.append(eng.portion(3, other[at2:at2 + c2], at2, list(range(c2))))
+        lg = eng.forward_portions(ps).cpu()
+        assert (lg[:c] - ref[at:at + c]).abs().max().item() < limit
+        if c2 > 0:
+            assert (lg[c:] - ref2[at2:at2 + c2]).abs().max().item() < limit
+        at, at2 = at + c, at2 + max(c2, 0)
