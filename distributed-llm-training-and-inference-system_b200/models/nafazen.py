@@ -191,6 +191,8 @@ class NafazenModel(nn.Module):
                 h = eops.postnorm_residual(y, x, blk.norm2, cfg.norm_eps, dt)
             if layer_trace is not None:
                 layer_trace.append(x.clone())
+        if batch.num_out == 0:                  # a step that only fills the caches
+            return torch.empty(0, cfg.vocab_size, dtype=torch.float32, device=x.device)
         y = eops.scalar_rmsnorm(x, batch.out_rows, self.final_norm, cfg.norm_eps, dt)
         if y.is_cuda and dt == torch.bfloat16 and ops.kernel_config().gemm == "native" and ops._gemm_ok(y, self.head) \
                 and self.head.shape[0] % 8 == 0:
