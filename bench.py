@@ -55,6 +55,10 @@ def parse_args():
     ap.add_argument("--extras-selftest", action="store_true", help="2 GPUs: run scaled-down extra arms (plumbing check)")
     ap.add_argument("--extra-steps", type=int, default=20)
     ap.add_argument("--extras-budget-s", type=float, default=420.0)
+    ap.add_argument("--arch-compare", default=None, choices=["nafazen"],
+                    help="1 GPU: serving throughput (prefill, decode) of this design beside a GPT of equal size, and its own "
+                         "kernels against the roofline; the default training workload is not run")
+    ap.add_argument("--arch-sizes", nargs="*", default=None, help="with --arch-compare: which built-in sizes (default all)")
     ap.add_argument("--gemm", default=None, help="override GEMM backend: native|cublas")
     ap.add_argument("--attention", default=None, help="override attention backend: native|sdpa")
     return ap.parse_args()
@@ -394,7 +398,10 @@ def main():
     if os.environ.get("LLMCTL_BENCH_FAULTHANDLER"):
         import faulthandler            # debugging aid: dump every thread's stack if the run is still alive after N seconds
         faulthandler.dump_traceback_later(float(os.environ["LLMCTL_BENCH_FAULTHANDLER"]), exit=True)
-    if args.impl == "reference":
+    if args.arch_compare:
+        from llmctl_b200.serve import arch_bench
+        res = arch_bench.run(args.arch_compare, args.arch_sizes)
+    elif args.impl == "reference":
         res = run_reference(args)
     else:
         res = run_native(args)

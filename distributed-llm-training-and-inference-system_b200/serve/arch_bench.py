@@ -1,0 +1,143 @@
+"""Serving throughput of a ragged-batch design (Nafazen) beside the GPT/LLaMA family at equal parameter count:
+prefill and decode tokens/s through ``InferenceEngine.generate`` (the scheduler, block manager and step function a
+user gets), random weights, a few layer sizes that resemble real models; plus device-timed runs of the design's own
+attention and grouped-GEMM kernels against the measured roofline.  ``bench.py --arch-compare nafazen`` prints the
+result as one JSON line.
+
+Reference: the reference's serving benchmark is ``llmctl bench e2e`` (reference llmctl/cli/commands/bench.py:98-160)."""
+from __future__ import annotations
+
+import json
+import time
+from pathlib import Path
+from typing import Any, Dict, List
+
+import torch
+
+SIZES: Dict[str, Dict[str, Any]] = {
+    # width, heads, latent sizes, feed-forwards; 4 layers: dense, MoE, dense, MoE (the last one reads layer 1's cache)
+    "w2048": dict(width=2048, vocab=32000, heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=512, q_rank=768, ff=8192,
+                  experts=8, top=2, expert_ff=2048, shared_ff=2048, pattern="aDbMaDcM"),
+    "w4096": dict(width=4096, vocab=32000, heads=32, dim=128, rot_dim=64, vdim=128, kv_rank=512, q_rank=1536, ff=14336,
+                  experts=16, top=2, expert_ff=1792, shared_ff=3584, pattern="aDbMaDcM"),
+}
+
+
+def _peaks() -> Dict[str, float]:
+    p = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    try:
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+    except Exception:  # noqa: BLE001
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def _gpt_equal(ncfg, params: int):
+    """A GPT configuration of the same width, depth, heads and vocabulary whose feed-forward width is chosen so that
+    the parameter counts match."""
+    from ..models.config import ModelConfig
+    L, W, H = len(ncfg.layers), ncfg.width, ncfg.layers[0].mixer.heads
+    hd = W // H
+    fixed = 2 * ncfg.vocab_size * W + L * (4 * W * H * hd + 2 * W) + W
+    ffn = max(256, int((params - fixed) / (3 * W * L)) // 128 * 128)
+    return ModelConfig(name=f"gpt-equal-{W}", layers=L, hidden=W, ffn=ffn, heads=H, head_dim=hd, vocab_size=ncfg.vocab_size,
+                       max_position_embeddings=8192)
+
+
+def _serve(cfg, prompts: List[List[int]], new_tokens: int, block_size: int) -> Dict[str, float]:
+    from .engine import InferenceEngine
+    total = sum(len(p) for p in prompts) + len(prompts) * (new_tokens + 1)
+    blocks = (total + block_size - 1) // block_size + 2 * len(prompts)
+    eng = InferenceEngine(cfg, max_batch_size=len(prompts), max_batch_tokens=max(8192, total), device="cuda", kv_block_size=block_size,
+                          num_kv_blocks=blocks)
+    out: Dict[str, float] = {}
+    for rnd in range(2):                   # the first round warms up (tensor maps, graphs, allocator)
+        for k in ("prefill_tokens", "decode_tokens", "prefill_time_s", "decode_time_s", "decode_steps"):
+            eng.stats[k] = 0 if "time" not in k else 0.0
+        torch.cuda.synchronize()
+        eng.generate(prompts, max_tokens=new_tokens if rnd else 4, temperature=0.0)
+        torch.cuda.synchronize()
+    s = eng.stats
+    out["prefill_tok_s"] = s["prefill_tokens"] / max(s["prefill_time_s"], 1e-9)
+    out["decode_tok_s"] = s["decode_tokens"] / max(s["decode_time_s"], 1e-9)
+    out["decode_ms_per_step"] = 1e3 * s["decode_time_s"] / max(s["decode_steps"], 1)
+    del eng
+    torch.cuda.empty_cache()
+    return out
+
+
+def _time(fn, iters: int = 10) -> float:
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters * 1e-3
+
+
+def _kernels(size: Dict[str, Any], peaks: Dict[str, float]) -> Dict[str, Any]:
+    """The design's own kernels in isolation (bf16): latent attention as prefill (2 x 2048 tokens) and as decode
+    (32 sequences at context 4096, cache larger than L2), and the grouped expert GEMM."""
+    from ..ops import latent_attention as L
+    from ..ops import moe as M
+    from ..ops import native
+    from ..ops.elementwise import rope_frequencies
+    from .ragged import Portion, RaggedBatch
+    dev = torch.device("cuda")
+    H, dn, dr, R = size["heads"], size["dim"], size["rot_dim"], size["kv_rank"]
+    bs, res = 64, {}
+    freq, mult = rope_frequencies(dr, 10000.0, None)
+    freq = freq.to(dev)
+    for name, nseq, ctx, new in (("prefill", 2, 2048, 2048), ("decode", 32, 4096, 1)):
+        per = (ctx + bs - 1) // bs
+        cache = torch.randn(nseq * per, bs, R + dr, device=dev).to(torch.bfloat16)
+        ps = [Portion(i, [0] * new, ctx - new, [], list(range(i * per, (i + 1) * per))) for i in range(nseq)]
+        b = RaggedBatch(ps, bs, dev)
+        T = b.num_tokens
+        ql = torch.randn(T, H, R, device=dev)
+        q = torch.randn(T, H * (dn + dr), device=dev).to(torch.bfloat16)
+        t = _time(lambda: L.latent_attention(ql, q, dn, cache, b.block_tables, b.tiles(H), b.positions, freq, mult, 0.07,
+                                             b.heads_per_tile(H), b.max_context, b.attention_splits(H)), 5)
+        keys = nseq * (ctx * new - new * (new - 1) // 2)                 # visible (query, key) pairs per head
+        flops = 2.0 * H * keys * (2 * R + dr)
+        bytes_ = nseq * ctx * (R + dr) * 2 + T * H * (R * 4 + R * 2)
+        res[f"latent_attention_{name}"] = {"ms": t * 1e3, "tflops": flops / t / 1e12, "gbs": bytes_ / t / 1e9,
+                                           "frac_of_bf16_peak": flops / t / 1e12 / peaks["bf16_tflops"],
+                                           "frac_of_hbm": bytes_ / t / 1e9 / peaks["hbm_gbs"]}
+    W, E, top, F = size["width"], size["experts"], size["top"], size["expert_ff"]
+    T = 4096
+    x = torch.randn(T, W, device=dev)
+    wr = torch.randn(E, W, device=dev).to(torch.bfloat16)
+    wgu = (torch.randn(E, 2 * F, W, device=dev) / W ** 0.5).to(torch.bfloat16)
+    wd = (torch.randn(E, W, F, device=dev) / F ** 0.5).to(torch.bfloat16)
+    t = _time(lambda: M.moe_ffn(x, torch.bfloat16, wr, wgu, wd, top, scale_input=True), 5)
+    flops = 2.0 * T * top * 3 * F * W
+    res["moe_ffn_4096_tokens"] = {"ms": t * 1e3, "tflops": flops / t / 1e12, "frac_of_bf16_peak": flops / t / 1e12 / peaks["bf16_tflops"]}
+    res["native_launches"] = native.launch_count
+    return res
+
+
+def run(which: str = "nafazen", sizes: List[str] | None = None, prompt_len: int = 1024, batch: int = 8, new_tokens: int = 64) -> Dict[str, Any]:
+    assert which == "nafazen"
+    from ..models.nafazen import NafazenConfig, example_config
+    peaks = _peaks()
+    out: Dict[str, Any] = {"metric": "serving_tokens_per_s", "design": which, "dtype": "bf16", "data": "synthetic, random weights",
+                           "workload": {"prompts": batch, "prompt_len": prompt_len, "new_tokens": new_tokens}, "peaks": peaks, "sizes": {}}
+    g = torch.Generator().manual_seed(0)
+    for name in sizes or list(SIZES):
+        size = SIZES[name]
+        ncfg = NafazenConfig.from_dict(example_config(**size), name=f"nafazen-{name}")
+        params = ncfg.num_parameters()
+        gcfg = _gpt_equal(ncfg, params)
+        prompts = [torch.randint(0, 32000, (prompt_len,), generator=g).tolist() for _ in range(batch)]
+        t0 = time.time()
+        row = {"params": params, "gpt_params": gcfg.num_parameters(), "gpt_ffn": gcfg.ffn,
+               "nafazen": _serve(ncfg, prompts, new_tokens, 64), "gpt": _serve(gcfg, prompts, new_tokens, 16),
+               "kernels": _kernels(size, peaks)}
+        row["seconds"] = round(time.time() - t0, 1)
+        out["sizes"][name] = row
+    return out

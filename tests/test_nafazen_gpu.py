@@ -138,11 +138,14 @@ def test_model_matches_oracle_on_gpu(cuda_device, dt):
     torch.manual_seed(5)
     toks = torch.randint(0, cfg["vocab"], (75,)).tolist()
     ref = oracle.forward(cfg, w, toks, exact=True)
-    limit = 3e-4 if dt == torch.float32 else 0.03 * float(ref.pow(2).mean().sqrt()) * 8      # bf16: a few % of the logits' rms, per element
+    def same(a, b):
+        if dt == torch.float32:
+            return (a - b).abs().max().item() < 3e-4
+        return float((a - b).pow(2).mean().sqrt() / b.pow(2).mean().sqrt()) < 0.05        # bf16: a few % of the logits' rms
     eng = _engine(copy.deepcopy(cfg), w, dt, "cuda")
     assert eng.kv.allocate(1, len(toks))
     got = eng.forward_portions([eng.portion(1, toks, 0, list(range(len(toks))))]).cpu()
-    assert (got - ref).abs().max().item() < limit
+    assert same(got, ref)
     eng.kv.free(1)
     # portions of 16 + 2 + 30, then decode; a second request rides along in the same batches
     other = toks[10:40]
@@ -157,7 +160,7 @@ def test_model_matches_oracle_on_gpu(cuda_device, dt):
             assert eng.kv.allocate(3, at2 + c2)
             ps.append(eng.portion(3, other[at2:at2 + c2], at2, list(range(c2))))
         lg = eng.forward_portions(ps).cpu()
-        assert (lg[:c] - ref[at:at + c]).abs().max().item() < limit
+        assert same(lg[:c], ref[at:at + c])
         if c2 > 0:
-            assert (lg[c:] - ref2[at2:at2 + c2]).abs().max().item() < limit
+            assert same(lg[c:], ref2[at2:at2 + c2])
         at, at2 = at + c, at2 + max(c2, 0)
