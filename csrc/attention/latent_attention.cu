@@ -19,9 +19,12 @@
 //                             softmax; the rotated query part is rotated on load.  Causal: a row at position p
 //                             sees cache positions 0..p of its sequence.  Long contexts are split over CTAs
 //                             (`splits` > 1) and merged by a second kernel, as the decode kernel in
-//                             csrc/serve/paged_attention.cu does.
+//                             csrc/serve/paged_attention.cu does.  bf16 with R + dr a multiple of 16 runs both
+//                             products on the tensor cores (mma.sync m16n8k16, fp32 accumulation; softmax, masks
+//                             and the running maximum / sum stay fp32); other sizes and fp32 run the FMA kernel.
 // Reference: none (the reference re-runs the HF model over the whole sequence, reference llmctl/serve/server.py:199-204).
 #include "../common/dtype.cuh"
+#include "../common/mma_sync.cuh"
 #include "../rope/rope_interleaved.cuh"
 
 namespace llmctl {
@@ -265,6 +268,213 @@ static int launch_latent_attention(const float* ql, const void* q, long long ldq
   return 0;
 }
 
+// ---- bf16 tensor-core variant ------------------------------------------------------------------------------------
+// Same tiling of the queries (16 rows per CTA); keys in tiles of 64 copied from the cache rows as they are.  Warp w
+// computes the scores of keys 16w..16w+15 (S = Q K^T over all R + dr columns), the softmax runs on S in shared memory,
+// P goes back as bf16 and warp w accumulates the columns [w * 8 NT, (w + 1) * 8 NT) of O += P C, where C is the first
+// R columns of the very same key tile (ldmatrix with transposition).
+constexpr int kTcKeys = 64;
+constexpr int kSsLd = kTcKeys + 4, kPsLd = kTcKeys + 8;
+
+template <int NT>
+__global__ void __launch_bounds__(kAttnThreads)
+latent_attention_tc_kernel(const float* __restrict__ ql, const __nv_bfloat16* __restrict__ q, long long ldq, int dn,
+                           const __nv_bfloat16* __restrict__ cache, const int* __restrict__ block_tables, int max_blocks,
+                           int block_size, const int* __restrict__ tiles, const int* __restrict__ positions,
+                           const float* __restrict__ freq, float mult, float scale, int H, int R, int dr, int heads_per_tile,
+                           int keys_per_split, __nv_bfloat16* __restrict__ out, float* __restrict__ partial) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int D = R + dr, Dp = D + 8;
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [kRows][Dp]
+  __nv_bfloat16* Ks = Qs + kRows * Dp;                                  // [kTcKeys][Dp]
+  float* Ss = reinterpret_cast<float*>(Ks + kTcKeys * Dp);              // [kRows][kSsLd]
+  __nv_bfloat16* Ps = reinterpret_cast<__nv_bfloat16*>(Ss + kRows * kSsLd);   // [kRows][kPsLd]
+  float* row_m = reinterpret_cast<float*>(Ps + kRows * kPsLd);
+  float* row_l = row_m + kRows;
+  float* row_c = row_l + kRows;
+  int* row_pos = reinterpret_cast<int*>(row_c + kRows);
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  const int* tile = tiles + 4 * blockIdx.x;
+  const int tok0 = tile[0], ntok = tile[1], seq = tile[2];
+  const int h0 = blockIdx.y * heads_per_tile;
+  const int nh = min(heads_per_tile, H - h0);
+  const int nrows = ntok * nh;
+  const int split = blockIdx.z, nsplit = gridDim.z;
+  const int* bt = block_tables + static_cast<long long>(seq) * max_blocks;
+
+  if (tid < kRows) {
+    row_m[tid] = -INFINITY;
+    row_l[tid] = 0.f;
+    row_c[tid] = 1.f;
+    row_pos[tid] = tid < nrows ? positions[tok0 + tid / nh] : -1;
+  }
+  __syncthreads();
+  for (int idx = tid; idx < kRows * D; idx += kAttnThreads) {
+    const int r = idx / D, c = idx % D;
+    float v = 0.f;
+    if (r < nrows) {
+      const int tok = tok0 + r / nh, h = h0 + r % nh;
+      if (c < R) {
+        v = ql[(static_cast<long long>(tok) * H + h) * R + c];
+      } else {
+        const __nv_bfloat16* qr = q + tok * ldq + static_cast<long long>(h) * (dn + dr) + dn;
+        v = rope_interleaved_coord([&](int k) { return to_f32(qr[k]); }, c - R, row_pos[r], freq, mult);
+      }
+    }
+    Qs[r * Dp + c] = __float2bfloat16(v);
+  }
+  float oacc[NT][4];
+#pragma unroll
+  for (int i = 0; i < NT; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) oacc[i][j] = 0.f;
+
+  const int last = row_pos[nrows - 1];
+  const int k_begin = split * keys_per_split;
+  const int k_end = min(last + 1, k_begin + keys_per_split);
+  const int vec_per_row = D >> 3;
+  for (int j0 = k_begin; j0 < k_end; j0 += kTcKeys) {
+    __syncthreads();
+    for (int idx = tid; idx < kTcKeys * vec_per_row; idx += kAttnThreads) {
+      const int jj = idx / vec_per_row, v = idx % vec_per_row, j = j0 + jj;
+      uint4 val = make_uint4(0u, 0u, 0u, 0u);
+      if (j < k_end) {
+        const long long slot = static_cast<long long>(bt[j / block_size]) * block_size + (j % block_size);
+        val = *reinterpret_cast<const uint4*>(cache + slot * D + v * 8);
+      }
+      *reinterpret_cast<uint4*>(Ks + jj * Dp + v * 8) = val;
+    }
+    __syncthreads();
+    {
+      float sacc[2][4] = {};
+      for (int k0 = 0; k0 < D; k0 += 16) {
+        uint32_t a[4];
+        load_a_frag(a, Qs, Dp, 0, k0, lane);
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          uint32_t b[2];
+          load_b_frag_nk(b, Ks, Dp, 16 * warp + 8 * nt, k0, lane);
+          mma_bf16_16816(sacc[nt], a, b);
+        }
+      }
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int r = g + (e >> 1) * 8, col = 16 * warp + 8 * nt + 2 * t + (e & 1), j = j0 + col;
+          Ss[r * kSsLd + col] = (j < k_end && j <= row_pos[r]) ? sacc[nt][e] * scale : -INFINITY;
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < kRows / 4; ++i) {
+      const int r = warp * (kRows / 4) + i;
+      const float s0 = Ss[r * kSsLd + lane], s1 = Ss[r * kSsLd + lane + 32];
+      const float m_old = row_m[r];
+      const float m_new = fmaxf(m_old, warp_max(fmaxf(s0, s1)));
+      const bool none = m_new == -INFINITY;
+      const float p0 = none ? 0.f : expf(s0 - m_new), p1 = none ? 0.f : expf(s1 - m_new);
+      const float corr = none ? 1.f : expf(m_old - m_new);
+      const float sum = warp_sum(p0 + p1);
+      Ps[r * kPsLd + lane] = __float2bfloat16(p0);
+      Ps[r * kPsLd + lane + 32] = __float2bfloat16(p1);
+      if (lane == 0) {
+        row_m[r] = m_new;
+        row_l[r] = row_l[r] * corr + sum;
+        row_c[r] = corr;
+      }
+    }
+    __syncthreads();
+    {
+      const float c_lo = row_c[g], c_hi = row_c[g + 8];
+#pragma unroll
+      for (int i = 0; i < NT; ++i) {
+        oacc[i][0] *= c_lo;
+        oacc[i][1] *= c_lo;
+        oacc[i][2] *= c_hi;
+        oacc[i][3] *= c_hi;
+      }
+#pragma unroll
+      for (int kk = 0; kk < kTcKeys / 16; ++kk) {
+        uint32_t a[4];
+        load_a_frag(a, Ps, kPsLd, 0, 16 * kk, lane);
+#pragma unroll
+        for (int i = 0; i < NT; ++i) {
+          const int n0 = 8 * (warp * NT + i);
+          if (n0 < R) {      // uniform over the warp
+            uint32_t b[2];
+            load_b_frag_kn(b, Ks, Dp, 16 * kk, n0, lane);
+            mma_bf16_16816(oacc[i], a, b);
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int r = g + 8 * half;
+    if (r >= nrows) continue;
+    const int tok = tok0 + r / nh, h = h0 + r % nh;
+    const long long base = static_cast<long long>(tok) * H + h;
+    const float inv = row_l[r] > 0.f ? 1.f / row_l[r] : 0.f;
+    float* dst = nsplit > 1 ? partial + (base * nsplit + split) * (R + 2) : nullptr;
+#pragma unroll
+    for (int i = 0; i < NT; ++i) {
+      const int c = 8 * (warp * NT + i) + 2 * t;
+      if (c < R) {
+        const float v0 = oacc[i][2 * half], v1 = oacc[i][2 * half + 1];
+        if (dst) {
+          dst[c] = v0;
+          dst[c + 1] = v1;
+        } else {
+          *reinterpret_cast<__nv_bfloat162*>(out + base * R + c) = __floats2bfloat162_rn(v0 * inv, v1 * inv);
+        }
+      }
+    }
+    if (dst && warp == 0 && t == 0) {
+      dst[R] = row_m[r];
+      dst[R + 1] = row_l[r];
+    }
+  }
+}
+
+static bool latent_attention_tc_ok(int R, int dr) {
+  const int D = R + dr;
+  const size_t smem = static_cast<size_t>(kRows + kTcKeys) * (D + 8) * 2 + kRows * kSsLd * 4 + kRows * kPsLd * 2 + 4 * kRows * 4;
+  return D % 16 == 0 && R % 8 == 0 && R <= 512 && smem <= 227 * 1024;
+}
+
+static int launch_latent_attention_tc(const float* ql, const void* q, long long ldq, int dn, const void* cache,
+                                      const int* block_tables, int max_blocks, int block_size, const int* tiles, int ntiles,
+                                      const int* positions, const float* freq, float mult, float scale, int H, int R, int dr,
+                                      int heads_per_tile, int splits, int keys_per_split, void* out, float* partial,
+                                      int tokens, cudaStream_t s) {
+  const int D = R + dr;
+  const size_t smem = static_cast<size_t>(kRows + kTcKeys) * (D + 8) * 2 + kRows * kSsLd * 4 + kRows * kPsLd * 2 + 4 * kRows * 4;
+  const int nt = (R + 31) / 32;
+  dim3 grid(ntiles, (H + heads_per_tile - 1) / heads_per_tile, splits);
+#define LAUNCH_TC(NT)                                                                                                \
+  do {                                                                                                               \
+    auto kern = latent_attention_tc_kernel<NT>;                                                                      \
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
+    if (e != cudaSuccess) return static_cast<int>(e);                                                                \
+    kern<<<grid, kAttnThreads, smem, s>>>(ql, (const __nv_bfloat16*)q, ldq, dn, (const __nv_bfloat16*)cache,         \
+                                          block_tables, max_blocks, block_size, tiles, positions, freq, mult, scale, \
+                                          H, R, dr, heads_per_tile, keys_per_split, (__nv_bfloat16*)out, partial);   \
+  } while (0)
+  if (nt <= 1) LAUNCH_TC(1);
+  else if (nt <= 2) LAUNCH_TC(2);
+  else if (nt <= 4) LAUNCH_TC(4);
+  else if (nt <= 8) LAUNCH_TC(8);
+  else LAUNCH_TC(16);
+#undef LAUNCH_TC
+  if (splits > 1)
+    latent_attention_merge_kernel<__nv_bfloat16><<<tokens * H, 128, 0, s>>>(partial, (__nv_bfloat16*)out, R, splits);
+  return 0;
+}
+
 }  // namespace llmctl
 
 using namespace llmctl;
@@ -286,12 +496,20 @@ LLMCTL_API int llmctl_latent_attention(const float* ql, const void* q, long long
                                        const int* block_tables, int max_blocks, int block_size, const int* tiles,
                                        int ntiles, int tokens, const int* positions, const float* freq, float mult,
                                        float scale, int H, int R, int dr, int heads_per_tile, int splits,
-                                       int keys_per_split, void* out, float* partial, int is_fp32, void* stream) {
+                                       int keys_per_split, void* out, float* partial, int is_fp32, int tensor_cores,
+                                       void* stream) {
   LLMCTL_BEGIN();
   LLMCTL_REQUIRE(H > 0 && R > 0 && dr >= 0 && dr % 2 == 0 && block_size > 0 && heads_per_tile >= 1 &&
                  heads_per_tile <= kRows && splits >= 1 && keys_per_split > 0 && (splits == 1 || partial != nullptr));
   if (ntiles == 0) return 0;
   int rc;
+  if (!is_fp32 && tensor_cores && latent_attention_tc_ok(R, dr) && keys_per_split % kTcKeys == 0) {
+    rc = launch_latent_attention_tc(ql, q, ldq, dn, cache, block_tables, max_blocks, block_size, tiles, ntiles, positions, freq,
+                                    mult, scale, H, R, dr, heads_per_tile, splits, keys_per_split, out, partial, tokens,
+                                    (cudaStream_t)stream);
+    if (rc != 0) LLMCTL_FAIL(rc, "latent attention launch");
+    LLMCTL_RETURN_LAST();
+  }
   LLMCTL_DISPATCH_DTYPE(is_fp32, T, (rc = launch_latent_attention<T>(ql, q, ldq, dn, cache, block_tables, max_blocks, block_size,
                                                                      tiles, ntiles, positions, freq, mult, scale, H, R, dr,
                                                                      heads_per_tile, splits, keys_per_split, out, partial,

@@ -11,11 +11,14 @@
 //                        routing weight when the weight applies to the expert's INPUT (scale_input), and records
 //                        where it went.
 //   llmctl_grouped_gemm: out[row, :] = A[row, :] W[expert(row)]^T over the permuted rows; a CTA computes a 64 x 64 tile
-//                        of one expert (row tiles never straddle experts thanks to the padding).
+//                        of one expert (row tiles never straddle experts thanks to the padding).  bf16 with K and N
+//                        multiples of 8 runs 64 x 128 tiles on the tensor cores (mma.sync m16n8k16, fp32 accumulation,
+//                        next k-slice prefetched into registers); fp32 and odd sizes run the FMA kernel.
 //   llmctl_moe_combine : y[t] = sum_k (w_k if the weight applies to the OUTPUT) * expert_out[row(t, k)]
 //                               + gate[t] * shared_out[t], in a fixed order (deterministic), fp32.
 // Reference: none (the reference has no model code).
 #include "../common/dtype.cuh"
+#include "../common/mma_sync.cuh"
 
 namespace llmctl {
 
@@ -156,6 +159,73 @@ grouped_gemm_kernel(const T* __restrict__ A, long long lda, const T* __restrict_
       if (n0 + tc + j < N) out[(row0 + tr + i) * ldo + n0 + tc + j] = from_f32<T>(acc[i][j]);
 }
 
+// bf16 tensor-core variant: 64 x 128 tile, 8 warps as 2 (rows) x 4 (columns), each 32 x 32.
+constexpr int kTcN = 128, kTcK = 32, kTcLd = kTcK + 8;
+
+__global__ void __launch_bounds__(256)
+grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const __nv_bfloat16* __restrict__ Wt,
+                       __nv_bfloat16* __restrict__ out, long long ldo, int N, int K, const int* __restrict__ meta, int E) {
+  const int tile = blockIdx.x;
+  if (tile >= meta[2 * E]) return;
+  const int e = meta[2 * E + 2 + tile];
+  const long long row0 = static_cast<long long>(tile) * kTileM;
+  const int n0 = blockIdx.y * kTcN;
+  const __nv_bfloat16* Bw = Wt + static_cast<long long>(e) * N * K;
+  __shared__ __align__(16) __nv_bfloat16 As[kTileM * kTcLd];
+  __shared__ __align__(16) __nv_bfloat16 Bs[kTcN * kTcLd];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  const int wm = warp >> 2, wn = warp & 3;
+  const int lr = tid >> 2, lv = tid & 3;          // this thread's row and 8-element slice within a k-slice
+  float acc[2][4][4] = {};
+  uint4 ra, rb[2];
+  auto fetch = [&](int k0) {
+    const int k = k0 + lv * 8;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    ra = k < K ? *reinterpret_cast<const uint4*>(A + (row0 + lr) * lda + k) : zero;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int n = n0 + lr + 64 * i;
+      rb[i] = (k < K && n < N) ? *reinterpret_cast<const uint4*>(Bw + static_cast<long long>(n) * K + k) : zero;
+    }
+  };
+  fetch(0);
+  for (int k0 = 0; k0 < K; k0 += kTcK) {
+    *reinterpret_cast<uint4*>(As + lr * kTcLd + lv * 8) = ra;
+    *reinterpret_cast<uint4*>(Bs + lr * kTcLd + lv * 8) = rb[0];
+    *reinterpret_cast<uint4*>(Bs + (lr + 64) * kTcLd + lv * 8) = rb[1];
+    __syncthreads();
+    if (k0 + kTcK < K) fetch(k0 + kTcK);
+#pragma unroll
+    for (int kk = 0; kk < kTcK; kk += 16) {
+      uint32_t a[2][4];
+#pragma unroll
+      for (int mi = 0; mi < 2; ++mi) load_a_frag(a[mi], As, kTcLd, 32 * wm + 16 * mi, kk, lane);
+#pragma unroll
+      for (int ni = 0; ni < 4; ++ni) {
+        uint32_t b[2];
+        load_b_frag_nk(b, Bs, kTcLd, 32 * wn + 8 * ni, kk, lane);
+#pragma unroll
+        for (int mi = 0; mi < 2; ++mi) mma_bf16_16816(acc[mi][ni], a[mi], b);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+    for (int ni = 0; ni < 4; ++ni) {
+      const int col = n0 + 32 * wn + 8 * ni + 2 * t;
+      if (col < N) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const long long row = row0 + 32 * wm + 16 * mi + g + 8 * half;
+          *reinterpret_cast<__nv_bfloat162*>(out + row * ldo + col) =
+              __floats2bfloat162_rn(acc[mi][ni][2 * half], acc[mi][ni][2 * half + 1]);
+        }
+      }
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const T* __restrict__ expert_out, int W, const int* __restrict__ pair_row,
@@ -212,6 +282,12 @@ LLMCTL_API int llmctl_grouped_gemm(const void* A, long long lda, const void* Wt,
   LLMCTL_BEGIN();
   LLMCTL_REQUIRE(N > 0 && K > 0 && lda >= K && ldo >= N);
   if (max_tiles == 0) return 0;
+  if (!is_fp32 && K % 8 == 0 && N % 8 == 0 && lda % 8 == 0 && ldo % 2 == 0 && (reinterpret_cast<uintptr_t>(A) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(Wt) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 3) == 0) {
+    grouped_gemm_tc_kernel<<<dim3(max_tiles, (N + kTcN - 1) / kTcN), 256, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)A, lda, (const __nv_bfloat16*)Wt, (__nv_bfloat16*)out, ldo, N, K, meta, E);
+    LLMCTL_RETURN_LAST();
+  }
   dim3 grid(max_tiles, (N + kTileN - 1) / kTileN);
   LLMCTL_DISPATCH_DTYPE(is_fp32, T, (grouped_gemm_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>(
                                         (const T*)A, lda, (const T*)Wt, (T*)out, ldo, N, K, meta, E)));

@@ -53,3 +53,19 @@ def run(
     if not ok:
         raise typer.Exit(1)
     return 0
+
+
+@app.command("trace")
+def trace(
+    model: Path = typer.Option(..., "--model", help="Directory with config.json and model.safetensors"),
+    out: Path = typer.Option(..., "--out", help="Directory for <step>.f32 logit files"),
+    max_tokens: int = typer.Option(..., "--max-tokens", help="Cache pool size in tokens (pages of 64)"),
+    dtype: str = typer.Option("bfloat16", "--dtype", help="bfloat16 | float32"),
+    device: Optional[str] = typer.Option(None, "--device"),
+):
+    """Replay a token-level trace from standard input (one JSON step per line) through the serving engine and write
+    the logits that the steps ask for (serve/replay.py; ``bin/trace_run`` is the same program)."""
+    from ...serve.replay import run as replay_trace
+    if dtype not in ("bfloat16", "float32"):
+        fail(f"--dtype must be bfloat16 or float32, not {dtype!r}", 2)
+    raise typer.Exit(replay_trace(str(model), dtype, str(out), max_tokens, device))

@@ -20,7 +20,7 @@ native.register_signature("llmctl_latent_kv_write", [c_void_p, c_ll, c_int, c_in
                                                       c_void_p, c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_void_p])
 native.register_signature("llmctl_latent_attention", [c_void_p, c_void_p, c_ll, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p,
                                                        c_int, c_int, c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_int,
-                                                       c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
+                                                       c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p])
 native._KERNELS_PER_CALL["llmctl_latent_attention"] = 1
 
 ROWS_PER_TILE = 16          # query rows (token, head) a CTA owns; tiles are built by the engine with this limit
@@ -54,7 +54,7 @@ def latent_kv_write(d: torch.Tensor, Q: int, R: int, dr: int, wq: torch.Tensor, 
 
 def latent_attention(ql: torch.Tensor, q: torch.Tensor, dn: int, cache: torch.Tensor, block_tables: torch.Tensor,
                      tiles: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor, mult: float, scale: float,
-                     heads_per_tile: int, max_context: int, splits: int = 1) -> torch.Tensor:
+                     heads_per_tile: int, max_context: int, splits: int = 1, tensor_cores: bool = True) -> torch.Tensor:
     """ql: fp32 [T, H, R] absorbed queries; q: [T, H * (dn + dr)] raw queries (the rope part of each head is rotated
     here); tiles: int32 [n, 4] = (first token row, tokens, block-table row, 0) with tokens * heads_per_tile <=
     ROWS_PER_TILE, all tokens of a tile in one sequence with growing positions.  Returns [T, H, R] in q's type:
@@ -68,12 +68,12 @@ def latent_attention(ql: torch.Tensor, q: torch.Tensor, dn: int, cache: torch.Te
         out = torch.empty(T, H, R, dtype=q.dtype, device=q.device)
         splits = max(1, int(splits))
         per = (max_context + splits - 1) // splits
-        per = max(32, (per + 31) // 32 * 32)
+        per = max(64, (per + 63) // 64 * 64)
         partial = torch.empty(T * H * splits * (R + 2), dtype=torch.float32, device=q.device) if splits > 1 else None
         native.call("llmctl_latent_attention", ql.data_ptr(), q.data_ptr(), q.stride(0), dn, cache.data_ptr(),
                     block_tables.data_ptr(), block_tables.shape[1], block_size, tiles.data_ptr(), tiles.shape[0], T,
                     positions.data_ptr(), freq.data_ptr(), float(mult), float(scale), H, R, dr, heads_per_tile, splits, per,
-                    out.data_ptr(), native.ptr(partial), _is32(q), native.stream_ptr())
+                    out.data_ptr(), native.ptr(partial), _is32(q), int(tensor_cores), native.stream_ptr())
         return out
     out = torch.zeros(T, H, R, dtype=torch.float32)
     rows = cache.view(-1, D).float()
