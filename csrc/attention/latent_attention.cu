@@ -75,7 +75,7 @@ constexpr int kAttnThreads = 128;
 // out: [tokens, H, R] (T) if gridDim.z == 1, else partial fp32 [tokens, H, splits, R + 2] = {acc, max, sum}
 template <typename T, int NC>
 __global__ void __launch_bounds__(kAttnThreads)
-latent_attention_kernel(const float* __restrict__ ql, const T* __restrict__ q, long long ldq, int dn,
+latent_attention_kernel(const float* __restrict__ ql, long long ql_st, long long ql_sh, const T* __restrict__ q, long long ldq, int dn,
                         const T* __restrict__ cache, const int* __restrict__ block_tables, int max_blocks,
                         int block_size, const int* __restrict__ tiles, const int* __restrict__ positions,
                         const float* __restrict__ freq, float mult, float scale, int H, int R, int dr, int heads_per_tile,
@@ -112,7 +112,7 @@ latent_attention_kernel(const float* __restrict__ ql, const T* __restrict__ q, l
     if (r < nrows) {
       const int tok = tok0 + r / nh, h = h0 + r % nh;
       if (c < R) {
-        v = ql[(static_cast<long long>(tok) * H + h) * R + c];
+        v = ql[tok * ql_st + h * ql_sh + c];
       } else {
         const T* qr = q + tok * ldq + static_cast<long long>(h) * (dn + dr) + dn;
         v = rope_interleaved_coord([&](int k) { return to_f32(qr[k]); }, c - R, row_pos[r], freq, mult);
@@ -238,7 +238,7 @@ latent_attention_merge_kernel(const float* __restrict__ partial, T* __restrict__
 }
 
 template <typename T>
-static int launch_latent_attention(const float* ql, const void* q, long long ldq, int dn, const void* cache,
+static int launch_latent_attention(const float* ql, long long ql_st, long long ql_sh, const void* q, long long ldq, int dn, const void* cache,
                                    const int* block_tables, int max_blocks, int block_size, const int* tiles, int ntiles,
                                    const int* positions, const float* freq, float mult, float scale, int H, int R, int dr,
                                    int heads_per_tile, int splits, int keys_per_split, void* out, float* partial,
@@ -253,7 +253,7 @@ static int launch_latent_attention(const float* ql, const void* q, long long ldq
     auto kern = latent_attention_kernel<T, NC>;                                                                      \
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
     if (e != cudaSuccess) return static_cast<int>(e);                                                                \
-    kern<<<grid, kAttnThreads, smem, s>>>(ql, (const T*)q, ldq, dn, (const T*)cache, block_tables, max_blocks,       \
+    kern<<<grid, kAttnThreads, smem, s>>>(ql, ql_st, ql_sh, (const T*)q, ldq, dn, (const T*)cache, block_tables, max_blocks, \
                                           block_size, tiles, positions, freq, mult, scale, H, R, dr, heads_per_tile, \
                                           keys_per_split, (T*)out, partial);                                         \
   } while (0)
@@ -276,9 +276,9 @@ static int launch_latent_attention(const float* ql, const void* q, long long ldq
 constexpr int kTcKeys = 64;
 constexpr int kSsLd = kTcKeys + 4, kPsLd = kTcKeys + 8;
 
-template <int NT>
+template <int NT, typename TQ>
 __global__ void __launch_bounds__(kAttnThreads)
-latent_attention_tc_kernel(const float* __restrict__ ql, const __nv_bfloat16* __restrict__ q, long long ldq, int dn,
+latent_attention_tc_kernel(const TQ* __restrict__ ql, long long ql_st, long long ql_sh, const __nv_bfloat16* __restrict__ q, long long ldq, int dn,
                            const __nv_bfloat16* __restrict__ cache, const int* __restrict__ block_tables, int max_blocks,
                            int block_size, const int* __restrict__ tiles, const int* __restrict__ positions,
                            const float* __restrict__ freq, float mult, float scale, int H, int R, int dr, int heads_per_tile,
@@ -316,7 +316,7 @@ latent_attention_tc_kernel(const float* __restrict__ ql, const __nv_bfloat16* __
     if (r < nrows) {
       const int tok = tok0 + r / nh, h = h0 + r % nh;
       if (c < R) {
-        v = ql[(static_cast<long long>(tok) * H + h) * R + c];
+        v = to_f32(ql[tok * ql_st + h * ql_sh + c]);
       } else {
         const __nv_bfloat16* qr = q + tok * ldq + static_cast<long long>(h) * (dn + dr) + dn;
         v = rope_interleaved_coord([&](int k) { return to_f32(qr[k]); }, c - R, row_pos[r], freq, mult);
@@ -446,7 +446,8 @@ static bool latent_attention_tc_ok(int R, int dr) {
   return D % 16 == 0 && R % 8 == 0 && R <= 512 && smem <= 227 * 1024;
 }
 
-static int launch_latent_attention_tc(const float* ql, const void* q, long long ldq, int dn, const void* cache,
+template <typename TQ>
+static int launch_latent_attention_tc(const TQ* ql, long long ql_st, long long ql_sh, const void* q, long long ldq, int dn, const void* cache,
                                       const int* block_tables, int max_blocks, int block_size, const int* tiles, int ntiles,
                                       const int* positions, const float* freq, float mult, float scale, int H, int R, int dr,
                                       int heads_per_tile, int splits, int keys_per_split, void* out, float* partial,
@@ -457,10 +458,10 @@ static int launch_latent_attention_tc(const float* ql, const void* q, long long 
   dim3 grid(ntiles, (H + heads_per_tile - 1) / heads_per_tile, splits);
 #define LAUNCH_TC(NT)                                                                                                \
   do {                                                                                                               \
-    auto kern = latent_attention_tc_kernel<NT>;                                                                      \
+    auto kern = latent_attention_tc_kernel<NT, TQ>;                                                                    \
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
     if (e != cudaSuccess) return static_cast<int>(e);                                                                \
-    kern<<<grid, kAttnThreads, smem, s>>>(ql, (const __nv_bfloat16*)q, ldq, dn, (const __nv_bfloat16*)cache,         \
+    kern<<<grid, kAttnThreads, smem, s>>>(ql, ql_st, ql_sh, (const __nv_bfloat16*)q, ldq, dn, (const __nv_bfloat16*)cache, \
                                           block_tables, max_blocks, block_size, tiles, positions, freq, mult, scale, \
                                           H, R, dr, heads_per_tile, keys_per_split, (__nv_bfloat16*)out, partial);   \
   } while (0)
@@ -492,7 +493,13 @@ LLMCTL_API int llmctl_latent_kv_write(const void* d, long long ld, int Q, int R,
 }
 
 // partial: fp32 scratch of tokens * H * splits * (R + 2) numbers when splits > 1 (may be null otherwise).
-LLMCTL_API int llmctl_latent_attention(const float* ql, const void* q, long long ldq, int dn, const void* cache,
+// ql: absorbed queries, element (token, head, c) at ql[token * ql_st + head * ql_sh + c]; fp32, or bf16 (ql_bf16) on the
+// tensor-core path only (llmctl_latent_attention_uses_tensor_cores).
+LLMCTL_API int llmctl_latent_attention_uses_tensor_cores(int is_fp32, int R, int dr) {
+  return (!is_fp32 && latent_attention_tc_ok(R, dr)) ? 1 : 0;
+}
+
+LLMCTL_API int llmctl_latent_attention(const void* ql, int ql_bf16, long long ql_st, long long ql_sh, const void* q, long long ldq, int dn, const void* cache,
                                        const int* block_tables, int max_blocks, int block_size, const int* tiles,
                                        int ntiles, int tokens, const int* positions, const float* freq, float mult,
                                        float scale, int H, int R, int dr, int heads_per_tile, int splits,
@@ -504,13 +511,19 @@ LLMCTL_API int llmctl_latent_attention(const float* ql, const void* q, long long
   if (ntiles == 0) return 0;
   int rc;
   if (!is_fp32 && tensor_cores && latent_attention_tc_ok(R, dr) && keys_per_split % kTcKeys == 0) {
-    rc = launch_latent_attention_tc(ql, q, ldq, dn, cache, block_tables, max_blocks, block_size, tiles, ntiles, positions, freq,
+    if (ql_bf16)
+      rc = launch_latent_attention_tc<__nv_bfloat16>((const __nv_bfloat16*)ql, ql_st, ql_sh, q, ldq, dn, cache, block_tables, max_blocks,
+                                                     block_size, tiles, ntiles, positions, freq, mult, scale, H, R, dr, heads_per_tile,
+                                                     splits, keys_per_split, out, partial, tokens, (cudaStream_t)stream);
+    else
+    rc = launch_latent_attention_tc<float>((const float*)ql, ql_st, ql_sh, q, ldq, dn, cache, block_tables, max_blocks, block_size, tiles, ntiles, positions, freq,
                                     mult, scale, H, R, dr, heads_per_tile, splits, keys_per_split, out, partial, tokens,
                                     (cudaStream_t)stream);
     if (rc != 0) LLMCTL_FAIL(rc, "latent attention launch");
     LLMCTL_RETURN_LAST();
   }
-  LLMCTL_DISPATCH_DTYPE(is_fp32, T, (rc = launch_latent_attention<T>(ql, q, ldq, dn, cache, block_tables, max_blocks, block_size,
+  LLMCTL_REQUIRE(!ql_bf16);
+  LLMCTL_DISPATCH_DTYPE(is_fp32, T, (rc = launch_latent_attention<T>((const float*)ql, ql_st, ql_sh, q, ldq, dn, cache, block_tables, max_blocks, block_size,
                                                                      tiles, ntiles, positions, freq, mult, scale, H, R, dr,
                                                                      heads_per_tile, splits, keys_per_split, out, partial,
                                                                      tokens, (cudaStream_t)stream)));

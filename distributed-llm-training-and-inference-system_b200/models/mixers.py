@@ -84,9 +84,17 @@ class LatentAttention(nn.Module):
         cq = lops.latent_kv_write(d, s.q_rank, s.kv_rank if own else 0, s.rot_dim if own else 0, self.q_norm, self.kv_norm,
                                   cache if own else None, batch.slots, batch.positions, self.rot_freq, self.rot_mult, self.eps)
         q = ops.linear(cq, self.w_uq)                                                   # [T, H * (dn + dr)]
-        qn = q.view(T, s.heads, s.dim + s.rot_dim)[:, :, :s.dim]
-        # absorbed queries in fp32: ql[t, h] = Uk_h^T qn[t, h]
-        ql = torch.bmm(qn.transpose(0, 1).float(), self.w_uk.float()).transpose(0, 1).contiguous()
+        qn = q.view(T, s.heads, s.dim + s.rot_dim)[:, :, :s.dim].transpose(0, 1)        # [H, T, dn], a view
+        # absorbed queries ql[t, h] = Uk_h^T qn[t, h]: fp32, except that the tensor-core attention kernel takes them
+        # in bf16 (it multiplies in bf16 anyway); the kernel reads the [H, T, R] product through its strides
+        if q.is_cuda and q.dtype == torch.bfloat16:
+            if lops.uses_tensor_cores(q.dtype, s.kv_rank, s.rot_dim):
+                ql = torch.bmm(qn, self.w_uk)
+            else:
+                ql = torch.bmm(qn, self.w_uk, out_dtype=torch.float32)
+        else:
+            ql = torch.bmm(qn.float(), self.w_uk.float())
+        ql = ql.transpose(0, 1)
         ol = lops.latent_attention(ql, q, s.dim, cache, batch.block_tables, batch.tiles(s.heads), batch.positions,
                                    self.rot_freq, self.rot_mult, s.scale, batch.heads_per_tile(s.heads), batch.max_context,
                                    batch.attention_splits(s.heads))

@@ -18,12 +18,18 @@ from .elementwise import _is32, rotate_interleaved
 c_void_p, c_int, c_ll, c_float = native.c_void_p, native.c_int, native.c_ll, native.c_float
 native.register_signature("llmctl_latent_kv_write", [c_void_p, c_ll, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                                       c_void_p, c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_void_p])
-native.register_signature("llmctl_latent_attention", [c_void_p, c_void_p, c_ll, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p,
+native.register_signature("llmctl_latent_attention", [c_void_p, c_int, c_ll, c_ll, c_void_p, c_ll, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p,
                                                        c_int, c_int, c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_int,
                                                        c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p])
 native._KERNELS_PER_CALL["llmctl_latent_attention"] = 1
 
 ROWS_PER_TILE = 16          # query rows (token, head) a CTA owns; tiles are built by the engine with this limit
+
+
+def uses_tensor_cores(dtype: torch.dtype, R: int, dr: int) -> bool:
+    """bf16 with these sizes runs the mma.sync kernel (which also takes bf16 absorbed queries); same rule as
+    llmctl_latent_attention_uses_tensor_cores."""
+    return dtype == torch.bfloat16 and (R + dr) % 16 == 0 and R % 8 == 0 and R <= 512
 
 
 def latent_kv_write(d: torch.Tensor, Q: int, R: int, dr: int, wq: torch.Tensor, wkv: Optional[torch.Tensor],
@@ -55,7 +61,7 @@ def latent_kv_write(d: torch.Tensor, Q: int, R: int, dr: int, wq: torch.Tensor, 
 def latent_attention(ql: torch.Tensor, q: torch.Tensor, dn: int, cache: torch.Tensor, block_tables: torch.Tensor,
                      tiles: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor, mult: float, scale: float,
                      heads_per_tile: int, max_context: int, splits: int = 1, tensor_cores: bool = True) -> torch.Tensor:
-    """ql: fp32 [T, H, R] absorbed queries; q: [T, H * (dn + dr)] raw queries (the rope part of each head is rotated
+    """ql: [T, H, R] absorbed queries (any token / head strides; fp32, or bf16 where ``uses_tensor_cores``); q: [T, H * (dn + dr)] raw queries (the rope part of each head is rotated
     here); tiles: int32 [n, 4] = (first token row, tokens, block-table row, 0) with tokens * heads_per_tile <=
     ROWS_PER_TILE, all tokens of a tile in one sequence with growing positions.  Returns [T, H, R] in q's type:
     softmax(scale * (ql . c + rot(qr) . kr)) c over cache positions 0..position of each token."""
@@ -64,13 +70,15 @@ def latent_attention(ql: torch.Tensor, q: torch.Tensor, dn: int, cache: torch.Te
     dr = D - R
     block_size = cache.shape[1]
     if q.is_cuda:
-        assert ql.dtype == torch.float32 and ql.is_contiguous() and q.stride(1) == 1 and cache.is_contiguous()
+        assert ql.stride(2) == 1 and q.stride(1) == 1 and cache.is_contiguous()
+        assert ql.dtype == torch.float32 or (tensor_cores and uses_tensor_cores(q.dtype, R, dr))
         out = torch.empty(T, H, R, dtype=q.dtype, device=q.device)
         splits = max(1, int(splits))
         per = (max_context + splits - 1) // splits
         per = max(64, (per + 63) // 64 * 64)
         partial = torch.empty(T * H * splits * (R + 2), dtype=torch.float32, device=q.device) if splits > 1 else None
-        native.call("llmctl_latent_attention", ql.data_ptr(), q.data_ptr(), q.stride(0), dn, cache.data_ptr(),
+        native.call("llmctl_latent_attention", ql.data_ptr(), int(ql.dtype == torch.bfloat16), ql.stride(0), ql.stride(1),
+                    q.data_ptr(), q.stride(0), dn, cache.data_ptr(),
                     block_tables.data_ptr(), block_tables.shape[1], block_size, tiles.data_ptr(), tiles.shape[0], T,
                     positions.data_ptr(), freq.data_ptr(), float(mult), float(scale), H, R, dr, heads_per_tile, splits, per,
                     out.data_ptr(), native.ptr(partial), _is32(q), int(tensor_cores), native.stream_ptr())
@@ -85,6 +93,6 @@ def latent_attention(ql: torch.Tensor, q: torch.Tensor, dn: int, cache: torch.Te
             j = torch.arange(p + 1)
             kv = rows[bt[j // block_size] * block_size + j % block_size]          # [p + 1, D]
             qr = rotate_interleaved(qh[t, :, dn:], positions[t:t + 1].expand(H), freq, mult)
-            s = (ql[t] @ kv[:, :R].t() + qr @ kv[:, R:].t()) * scale
+            s = (ql[t].float() @ kv[:, :R].t() + qr @ kv[:, R:].t()) * scale
             out[t] = torch.softmax(s, -1) @ kv[:, :R]
     return out.to(q.dtype)
