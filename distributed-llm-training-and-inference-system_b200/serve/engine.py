@@ -341,10 +341,45 @@ class InferenceEngine:
         """The step function of ragged models: run the given portions (each sequence's next tokens; its cache blocks
         must already cover them) as one batch; returns fp32 logits [total wanted positions, vocab]."""
         assert self.ragged, "forward_portions serves models that declare ragged = True"
+        if (self.cuda_graphs and layer_trace is None and all(len(p.tokens) == 1 and list(p.want) == [0] for p in portions)
+                and len(portions) <= self.max_batch_size):
+            return self._replay_ragged_decode(portions)
         batch = RaggedBatch(portions, self.block_size, self.device)
         self.stats["batch_tokens"] = self.stats.get("batch_tokens", 0) + batch.num_tokens
         self.stats["h2d_bytes"] = self.stats.get("h2d_bytes", 0) + batch.nbytes
         return self.model.forward_ragged(batch, self.caches, layer_trace)
+
+    def _replay_ragged_decode(self, portions: List[Portion]) -> torch.Tensor:
+        """A step in which every sequence decodes one token: the batch is padded to a (sequences, block-table columns)
+        bucket whose buffers keep their addresses, and the whole step is a CUDA graph captured on first use."""
+        B = len(portions)
+        ctx = max(p.start + 1 for p in portions)
+        Bb = self._bucket(B, 1, max(self.max_batch_size, 1))
+        cb = self._bucket(ctx, 256, max(self.max_context, ctx))
+        max_blocks = max((cb + self.block_size - 1) // self.block_size, max(len(p.block_table) for p in portions))
+        key = ("ragged", Bb, max_blocks)
+        g = self._graphs.get(key)
+        self.stats["batch_tokens"] = self.stats.get("batch_tokens", 0) + B
+        if g is None:
+            if len(self._graphs) > 64:
+                self._graphs.clear()
+            batch = RaggedBatch(portions, self.block_size, self.device, pad_to=(Bb, max_blocks, max_blocks * self.block_size))
+            side = torch.cuda.Stream(device=self.device)
+            side.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(side):
+                for _ in range(2):                          # warm-up: lazy inits, workspaces, cuBLAS handles
+                    self.model.forward_ragged(batch, self.caches)
+            torch.cuda.current_stream(self.device).wait_stream(side)
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                logits = self.model.forward_ragged(batch, self.caches)
+            g = self._graphs[key] = (batch, graph, logits)
+        else:
+            g[0].refill(portions)
+        self.stats["h2d_bytes"] = self.stats.get("h2d_bytes", 0) + g[0].nbytes
+        g[1].replay()
+        return g[2][:B]
 
     def portion(self, seq_id: int, tokens: List[int], start: int, want: List[int]) -> Portion:
         return Portion(seq_id, tokens, start, want, self.kv.block_table(seq_id))

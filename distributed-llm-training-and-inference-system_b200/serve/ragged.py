@@ -8,7 +8,7 @@ Reference: the reference right-pads a batch and recomputes whole sequences (refe
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import List, Sequence as Seq, Tuple
+from typing import List, Optional, Sequence as Seq, Tuple
 
 import numpy as np
 import torch
@@ -28,47 +28,38 @@ class Portion:
 
 
 class RaggedBatch:
-    def __init__(self, portions: List[Portion], block_size: int, device: torch.device, sm_count: int = 148):
-        T = sum(len(p.tokens) for p in portions)
-        B = len(portions)
-        assert T > 0
+    """``pad_to = (sequences, block-table columns, context bound)`` fixes the shape of a decode-only batch: missing
+    sequences become padding rows (token 0 at position 0, no cache slot, logits ignored), and ``refill`` rewrites the
+    same pinned and device buffers for the next step, so that the step can be captured once and replayed as a CUDA
+    graph."""
+
+    def __init__(self, portions: List[Portion], block_size: int, device: torch.device, sm_count: int = 148,
+                 pad_to: Optional[Tuple[int, int, int]] = None):
+        self.block_size, self.device, self._sms, self.pad_to = block_size, device, sm_count, pad_to
         self.decode_only = all(len(p.tokens) == 1 for p in portions)
         self.tokens_per_tile = 1 if self.decode_only else ROWS_PER_TILE
-        self.max_context = max(p.start + len(p.tokens) for p in portions)
-        max_blocks = max(len(p.block_table) for p in portions)
-        n_out = sum(len(p.want) for p in portions)
-        ntiles = sum((len(p.tokens) + self.tokens_per_tile - 1) // self.tokens_per_tile for p in portions)
+        if pad_to is not None:
+            assert self.decode_only and len(portions) <= pad_to[0]
+            T = B = n_out = ntiles = pad_to[0]
+            max_blocks, self.max_context = pad_to[1], pad_to[2]
+        else:
+            T = sum(len(p.tokens) for p in portions)
+            B = len(portions)
+            assert T > 0
+            self.max_context = max(p.start + len(p.tokens) for p in portions)
+            max_blocks = max(len(p.block_table) for p in portions)
+            n_out = sum(len(p.want) for p in portions)
+            ntiles = sum((len(p.tokens) + self.tokens_per_tile - 1) // self.tokens_per_tile for p in portions)
         # int32 words: tokens(2T) | slots(2T) | out_rows(2 n_out) | positions(T) | tiles(4 ntiles) | block tables(B max_blocks)
         sizes = [2 * T, 2 * T, 2 * n_out, T, 4 * ntiles, B * max_blocks]
         offs = np.concatenate([[0], np.cumsum(sizes)])
-        host = torch.zeros(int(offs[-1]), dtype=torch.int32, pin_memory=device.type == "cuda")
-        a = host.numpy()
-        tokens = a[offs[0]:offs[1]].view(np.int64)
-        slots = a[offs[1]:offs[2]].view(np.int64)
-        out_rows = a[offs[2]:offs[3]].view(np.int64)
-        positions = a[offs[3]:offs[4]]
-        tiles = a[offs[4]:offs[5]].reshape(ntiles, 4)
-        tables = a[offs[5]:offs[6]].reshape(B, max_blocks)
-        t = o = ti = 0
-        for b, p in enumerate(portions):
-            n = len(p.tokens)
-            bt = np.asarray(p.block_table, dtype=np.int64)
-            pos = np.arange(p.start, p.start + n)
-            assert len(bt) * block_size >= p.start + n, "the sequence owns too few cache blocks for this portion"
-            tokens[t:t + n] = np.asarray(p.tokens, dtype=np.int64)
-            positions[t:t + n] = pos
-            slots[t:t + n] = bt[pos // block_size] * block_size + pos % block_size
-            tables[b, :len(bt)] = bt
-            for w in p.want:
-                assert 0 <= w < n
-                out_rows[o] = t + w
-                o += 1
-            for s in range(0, n, self.tokens_per_tile):
-                tiles[ti] = (t + s, min(self.tokens_per_tile, n - s), b, 0)
-                ti += 1
-            t += n
-        dev = host.to(device, non_blocking=True) if device.type == "cuda" else host
-        self.nbytes = host.numel() * 4
+        self._host = torch.zeros(int(offs[-1]), dtype=torch.int32, pin_memory=device.type == "cuda")
+        a = self._host.numpy()
+        self._h = (a[offs[0]:offs[1]].view(np.int64), a[offs[1]:offs[2]].view(np.int64), a[offs[2]:offs[3]].view(np.int64),
+                   a[offs[3]:offs[4]], a[offs[4]:offs[5]].reshape(ntiles, 4), a[offs[5]:offs[6]].reshape(B, max_blocks))
+        dev = torch.empty_like(self._host, device=device) if device.type == "cuda" else self._host
+        self._dev = dev
+        self.nbytes = self._host.numel() * 4
         self.num_tokens, self.num_out, self.num_tiles = T, n_out, ntiles
         self.tokens = dev[offs[0]:offs[1]].view(torch.int64)
         self.slots = dev[offs[1]:offs[2]].view(torch.int64)
@@ -76,8 +67,43 @@ class RaggedBatch:
         self.positions = dev[offs[3]:offs[4]]
         self._tiles = dev[offs[4]:offs[5]].view(ntiles, 4)
         self.block_tables = dev[offs[5]:offs[6]].view(B, max_blocks)
-        self._sms = sm_count
-        self._host = host      # keeps the pinned buffer alive until the copy has run
+        self.refill(portions)
+
+    def refill(self, portions: List[Portion]) -> None:
+        """Write the description of ``portions`` into the (same) buffers and copy it to the device."""
+        tokens, slots, out_rows, positions, tiles, tables = self._h
+        block_size = self.block_size
+        if self.pad_to is not None:
+            assert len(portions) <= self.pad_to[0] and all(len(p.tokens) == 1 for p in portions)
+            tokens[:] = 0
+            slots[:] = -1
+            positions[:] = 0
+            tables[:] = 0
+            for r in range(self.pad_to[0]):                 # padding rows too: one tile and one (ignored) logits row each
+                tiles[r] = (r, 1, r, 0)
+                out_rows[r] = r
+        t = o = ti = 0
+        for b, p in enumerate(portions):
+            n = len(p.tokens)
+            bt = np.asarray(p.block_table, dtype=np.int64)
+            pos = np.arange(p.start, p.start + n)
+            assert len(bt) * block_size >= p.start + n, "the sequence owns too few cache blocks for this portion"
+            assert len(bt) <= tables.shape[1] and p.start + n <= max(self.max_context, 1)
+            tokens[t:t + n] = np.asarray(p.tokens, dtype=np.int64)
+            positions[t:t + n] = pos
+            slots[t:t + n] = bt[pos // block_size] * block_size + pos % block_size
+            tables[b, :len(bt)] = bt
+            if self.pad_to is None:
+                for w in p.want:
+                    assert 0 <= w < n
+                    out_rows[o] = t + w
+                    o += 1
+                for s in range(0, n, self.tokens_per_tile):
+                    tiles[ti] = (t + s, min(self.tokens_per_tile, n - s), b, 0)
+                    ti += 1
+            t += n
+        if self._dev is not self._host:
+            self._dev.copy_(self._host, non_blocking=True)
 
     # ---- attention tiling -----------------------------------------------------------------------------------
     def tiles(self, heads: int) -> torch.Tensor:

@@ -165,3 +165,32 @@ def test_model_matches_oracle_on_gpu(cuda_device, dt):
         if c2 > 0:
             assert same(lg[c:], ref2[at2:at2 + c2])
         at, at2 = at + c, at2 + max(c2, 0)
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+def test_greedy_generation_with_replayed_decode_graph(cuda_device, dt):
+    """``InferenceEngine.generate`` with the decode step replayed as a CUDA graph (padded batch, fixed buffers): unequal
+    requests, block growth across pages, sequences finishing at different steps; tokens = the oracle's argmax."""
+    from llmctl_b200.models.nafazen import example_config
+    from llmctl_b200.serve.engine import InferenceEngine
+    cfg = example_config(pattern="aDbMcM", softcap=None)
+    w = oracle.random_weights(cfg, seed=21)
+    eng = InferenceEngine(copy.deepcopy(cfg), max_batch_size=4, max_batch_tokens=1024, device="cuda", kv_block_size=16, num_kv_blocks=40,
+                          dtype=dt, kv_watermark=0.0, cuda_graphs=True)
+    eng.model.load_state(w)
+    g = torch.Generator().manual_seed(7)
+    prompts = [torch.randint(0, cfg["vocab"], (n,), generator=g).tolist() for n in (5, 30, 1)]
+    seqs = [eng.add_request(p, max_tokens=m, temperature=0.0) for p, m in zip(prompts, (50, 20, 35))]
+    while eng.has_work():
+        eng.step()
+    assert any(k[0] == "ragged" for k in eng._graphs if isinstance(k[0], str)), "the decode graph was never used"
+    gap = 1e-3 if dt == torch.float32 else 0.15
+    for p, s in zip(prompts, seqs):
+        o = s.generated
+        ref = oracle.forward(cfg, w, p + o, exact=True)
+        top2 = ref.topk(2, -1).values
+        for k, tok in enumerate(o):
+            row = len(p) + k - 1
+            if top2[row, 0] - top2[row, 1] > gap:
+                assert tok == int(ref[row].argmax()), f"token {k} of prompt len {len(p)}"
+    assert eng.kv.free_blocks == 40
