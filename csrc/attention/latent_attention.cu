@@ -310,19 +310,19 @@ latent_attention_tc_kernel(const TQ* __restrict__ ql, long long ql_st, long long
     row_pos[tid] = tid < nrows ? positions[tok0 + tid / nh] : -1;
   }
   __syncthreads();
-  for (int idx = tid; idx < kRows * D; idx += kAttnThreads) {
-    const int r = idx / D, c = idx % D;
-    float v = 0.f;
+  for (int r = warp; r < kRows; r += kAttnThreads / 32) {     // a warp per query row
+    __nv_bfloat16* dst = Qs + r * Dp;
     if (r < nrows) {
       const int tok = tok0 + r / nh, h = h0 + r % nh;
-      if (c < R) {
-        v = to_f32(ql[tok * ql_st + h * ql_sh + c]);
-      } else {
-        const __nv_bfloat16* qr = q + tok * ldq + static_cast<long long>(h) * (dn + dr) + dn;
-        v = rope_interleaved_coord([&](int k) { return to_f32(qr[k]); }, c - R, row_pos[r], freq, mult);
-      }
+      const TQ* src = ql + tok * ql_st + h * ql_sh;
+      for (int c = lane; c < R; c += 32) dst[c] = __float2bfloat16(to_f32(src[c]));
+      const __nv_bfloat16* qr = q + tok * ldq + static_cast<long long>(h) * (dn + dr) + dn;
+      const int pos = row_pos[r];
+      for (int c = lane; c < dr; c += 32)
+        dst[R + c] = __float2bfloat16(rope_interleaved_coord([&](int k) { return to_f32(qr[k]); }, c, pos, freq, mult));
+    } else {
+      for (int c = lane; c < D; c += 32) dst[c] = __float2bfloat16(0.f);
     }
-    Qs[r * Dp + c] = __float2bfloat16(v);
   }
   float oacc[NT][4];
 #pragma unroll
@@ -336,15 +336,19 @@ latent_attention_tc_kernel(const TQ* __restrict__ ql, long long ql_st, long long
   const int vec_per_row = D >> 3;
   for (int j0 = k_begin; j0 < k_end; j0 += kTcKeys) {
     __syncthreads();
-    for (int idx = tid; idx < kTcKeys * vec_per_row; idx += kAttnThreads) {
-      const int jj = idx / vec_per_row, v = idx % vec_per_row, j = j0 + jj;
-      uint4 val = make_uint4(0u, 0u, 0u, 0u);
+    for (int jj = warp; jj < kTcKeys; jj += kAttnThreads / 32) {   // a warp per key row, asynchronous 16-byte copies
+      const int j = j0 + jj;
+      __nv_bfloat16* dst = Ks + jj * Dp;
       if (j < k_end) {
         const long long slot = static_cast<long long>(bt[j / block_size]) * block_size + (j % block_size);
-        val = *reinterpret_cast<const uint4*>(cache + slot * D + v * 8);
+        const __nv_bfloat16* src = cache + slot * D;
+        for (int v = lane; v < vec_per_row; v += 32) cp_async_16(dst + v * 8, src + v * 8);
+      } else {
+        for (int v = lane; v < vec_per_row; v += 32) *reinterpret_cast<uint4*>(dst + v * 8) = make_uint4(0u, 0u, 0u, 0u);
       }
-      *reinterpret_cast<uint4*>(Ks + jj * Dp + v * 8) = val;
     }
+    cp_async_commit();
+    cp_async_wait_all();
     __syncthreads();
     {
       float sacc[2][4] = {};

@@ -118,4 +118,4 @@ class RaggedBatch:
         """Split the keys of long contexts over CTAs when the tiles alone would leave most SMs idle."""
         hpt = self.heads_per_tile(heads)
         ctas = self.num_tiles * ((heads + hpt - 1) // hpt)
-        return int(max(1, min(2 * self._sms // max(ctas, 1), self.max_context // 128)))
+        return int(max(1, min(2 * self._sms // max(ctas, 1), self.max_context // 64)))
