@@ -269,15 +269,16 @@ static int launch_latent_attention(const float* ql, long long ql_st, long long q
 }
 
 // ---- bf16 tensor-core variant ------------------------------------------------------------------------------------
-// Same tiling of the queries (16 rows per CTA); keys in tiles of 64 copied from the cache rows as they are.  Warp w
-// computes the scores of keys 16w..16w+15 (S = Q K^T over all R + dr columns), the softmax runs on S in shared memory,
+// Same tiling of the queries (16 rows per CTA, 8 warps); keys in tiles of 64 copied from the cache rows as they are.  Warp w
+// computes the scores of keys 8w..8w+7 (S = Q K^T over all R + dr columns), the softmax runs on S in shared memory,
 // P goes back as bf16 and warp w accumulates the columns [w * 8 NT, (w + 1) * 8 NT) of O += P C, where C is the first
 // R columns of the very same key tile (ldmatrix with transposition).
 constexpr int kTcKeys = 64;
+constexpr int kTcThreads = 256, kTcWarps = kTcThreads / 32;
 constexpr int kSsLd = kTcKeys + 4, kPsLd = kTcKeys + 8;
 
 template <int NT, typename TQ>
-__global__ void __launch_bounds__(kAttnThreads)
+__global__ void __launch_bounds__(kTcThreads)
 latent_attention_tc_kernel(const TQ* __restrict__ ql, long long ql_st, long long ql_sh, const __nv_bfloat16* __restrict__ q, long long ldq, int dn,
                            const __nv_bfloat16* __restrict__ cache, const int* __restrict__ block_tables, int max_blocks,
                            int block_size, const int* __restrict__ tiles, const int* __restrict__ positions,
@@ -310,7 +311,7 @@ latent_attention_tc_kernel(const TQ* __restrict__ ql, long long ql_st, long long
     row_pos[tid] = tid < nrows ? positions[tok0 + tid / nh] : -1;
   }
   __syncthreads();
-  for (int r = warp; r < kRows; r += kAttnThreads / 32) {     // a warp per query row
+  for (int r = warp; r < kRows; r += kTcWarps) {     // a warp per query row
     __nv_bfloat16* dst = Qs + r * Dp;
     if (r < nrows) {
       const int tok = tok0 + r / nh, h = h0 + r % nh;
@@ -336,7 +337,7 @@ latent_attention_tc_kernel(const TQ* __restrict__ ql, long long ql_st, long long
   const int vec_per_row = D >> 3;
   for (int j0 = k_begin; j0 < k_end; j0 += kTcKeys) {
     __syncthreads();
-    for (int jj = warp; jj < kTcKeys; jj += kAttnThreads / 32) {   // a warp per key row, asynchronous 16-byte copies
+    for (int jj = warp; jj < kTcKeys; jj += kTcWarps) {   // a warp per key row, asynchronous 16-byte copies
       const int j = j0 + jj;
       __nv_bfloat16* dst = Ks + jj * Dp;
       if (j < k_end) {
@@ -351,29 +352,23 @@ latent_attention_tc_kernel(const TQ* __restrict__ ql, long long ql_st, long long
     cp_async_wait_all();
     __syncthreads();
     {
-      float sacc[2][4] = {};
+      float sacc[4] = {};
       for (int k0 = 0; k0 < D; k0 += 16) {
-        uint32_t a[4];
+        uint32_t a[4], b[2];
         load_a_frag(a, Qs, Dp, 0, k0, lane);
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-          uint32_t b[2];
-          load_b_frag_nk(b, Ks, Dp, 16 * warp + 8 * nt, k0, lane);
-          mma_bf16_16816(sacc[nt], a, b);
-        }
+        load_b_frag_nk(b, Ks, Dp, 8 * warp, k0, lane);
+        mma_bf16_16816(sacc, a, b);
       }
 #pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int r = g + (e >> 1) * 8, col = 16 * warp + 8 * nt + 2 * t + (e & 1), j = j0 + col;
-          Ss[r * kSsLd + col] = (j < k_end && j <= row_pos[r]) ? sacc[nt][e] * scale : -INFINITY;
-        }
+      for (int e = 0; e < 4; ++e) {
+        const int r = g + (e >> 1) * 8, col = 8 * warp + 2 * t + (e & 1), j = j0 + col;
+        Ss[r * kSsLd + col] = (j < k_end && j <= row_pos[r]) ? sacc[e] * scale : -INFINITY;
+      }
     }
     __syncthreads();
 #pragma unroll
-    for (int i = 0; i < kRows / 4; ++i) {
-      const int r = warp * (kRows / 4) + i;
+    for (int i = 0; i < kRows / kTcWarps; ++i) {
+      const int r = warp * (kRows / kTcWarps) + i;
       const float s0 = Ss[r * kSsLd + lane], s1 = Ss[r * kSsLd + lane + 32];
       const float m_old = row_m[r];
       const float m_new = fmaxf(m_old, warp_max(fmaxf(s0, s1)));
@@ -458,22 +453,21 @@ static int launch_latent_attention_tc(const TQ* ql, long long ql_st, long long q
                                       int tokens, cudaStream_t s) {
   const int D = R + dr;
   const size_t smem = static_cast<size_t>(kRows + kTcKeys) * (D + 8) * 2 + kRows * kSsLd * 4 + kRows * kPsLd * 2 + 4 * kRows * 4;
-  const int nt = (R + 31) / 32;
+  const int nt = (R + 8 * kTcWarps - 1) / (8 * kTcWarps);
   dim3 grid(ntiles, (H + heads_per_tile - 1) / heads_per_tile, splits);
 #define LAUNCH_TC(NT)                                                                                                \
   do {                                                                                                               \
     auto kern = latent_attention_tc_kernel<NT, TQ>;                                                                    \
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
     if (e != cudaSuccess) return static_cast<int>(e);                                                                \
-    kern<<<grid, kAttnThreads, smem, s>>>(ql, ql_st, ql_sh, (const __nv_bfloat16*)q, ldq, dn, (const __nv_bfloat16*)cache, \
+    kern<<<grid, kTcThreads, smem, s>>>(ql, ql_st, ql_sh, (const __nv_bfloat16*)q, ldq, dn, (const __nv_bfloat16*)cache, \
                                           block_tables, max_blocks, block_size, tiles, positions, freq, mult, scale, \
                                           H, R, dr, heads_per_tile, keys_per_split, (__nv_bfloat16*)out, partial);   \
   } while (0)
   if (nt <= 1) LAUNCH_TC(1);
   else if (nt <= 2) LAUNCH_TC(2);
   else if (nt <= 4) LAUNCH_TC(4);
-  else if (nt <= 8) LAUNCH_TC(8);
-  else LAUNCH_TC(16);
+  else LAUNCH_TC(8);
 #undef LAUNCH_TC
   if (splits > 1)
     latent_attention_merge_kernel<__nv_bfloat16><<<tokens * H, 128, 0, s>>>(partial, (__nv_bfloat16*)out, R, splits);
