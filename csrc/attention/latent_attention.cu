@@ -274,28 +274,32 @@ static int launch_latent_attention(const float* ql, long long ql_st, long long q
 // P goes back as bf16 and warp w accumulates the columns [w * 8 NT, (w + 1) * 8 NT) of O += P C, where C is the first
 // R columns of the very same key tile (ldmatrix with transposition).
 constexpr int kTcKeys = 64;
-constexpr int kTcThreads = 256, kTcWarps = kTcThreads / 32;
 constexpr int kSsLd = kTcKeys + 4, kPsLd = kTcKeys + 8;
 
-template <int NT, typename TQ>
-__global__ void __launch_bounds__(kTcThreads)
+// MT row tiles of 16 query rows per CTA and 8 MT warps: warp (wm, wn) = (warp / 8, warp % 8) owns row tile wm, the
+// scores of keys 8 wn .. 8 wn + 7 and the output columns [8 NT wn, 8 NT (wn + 1)).  MT = 2 halves the key traffic
+// per query row (prompt portions: 32 tokens per tile; decoding with more than 16 heads: 32 heads per tile).
+template <int NT, int MT, typename TQ>
+__global__ void __launch_bounds__(256 * MT)
 latent_attention_tc_kernel(const TQ* __restrict__ ql, long long ql_st, long long ql_sh, const __nv_bfloat16* __restrict__ q, long long ldq, int dn,
                            const __nv_bfloat16* __restrict__ cache, const int* __restrict__ block_tables, int max_blocks,
                            int block_size, const int* __restrict__ tiles, const int* __restrict__ positions,
                            const float* __restrict__ freq, float mult, float scale, int H, int R, int dr, int heads_per_tile,
                            int keys_per_split, __nv_bfloat16* __restrict__ out, float* __restrict__ partial) {
+  constexpr int kR = 16 * MT, kWarps = 8 * MT;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int D = R + dr, Dp = D + 8;
-  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [kRows][Dp]
-  __nv_bfloat16* Ks = Qs + kRows * Dp;                                  // [kTcKeys][Dp]
-  float* Ss = reinterpret_cast<float*>(Ks + kTcKeys * Dp);              // [kRows][kSsLd]
-  __nv_bfloat16* Ps = reinterpret_cast<__nv_bfloat16*>(Ss + kRows * kSsLd);   // [kRows][kPsLd]
-  float* row_m = reinterpret_cast<float*>(Ps + kRows * kPsLd);
-  float* row_l = row_m + kRows;
-  float* row_c = row_l + kRows;
-  int* row_pos = reinterpret_cast<int*>(row_c + kRows);
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [kR][Dp]
+  __nv_bfloat16* Ks = Qs + kR * Dp;                                     // [kTcKeys][Dp]
+  float* Ss = reinterpret_cast<float*>(Ks + kTcKeys * Dp);              // [kR][kSsLd]
+  __nv_bfloat16* Ps = reinterpret_cast<__nv_bfloat16*>(Ss + kR * kSsLd);      // [kR][kPsLd]
+  float* row_m = reinterpret_cast<float*>(Ps + kR * kPsLd);
+  float* row_l = row_m + kR;
+  float* row_c = row_l + kR;
+  int* row_pos = reinterpret_cast<int*>(row_c + kR);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  const int wm = warp >> 3, wn = warp & 7;
   const int* tile = tiles + 4 * blockIdx.x;
   const int tok0 = tile[0], ntok = tile[1], seq = tile[2];
   const int h0 = blockIdx.y * heads_per_tile;
@@ -304,14 +308,14 @@ latent_attention_tc_kernel(const TQ* __restrict__ ql, long long ql_st, long long
   const int split = blockIdx.z, nsplit = gridDim.z;
   const int* bt = block_tables + static_cast<long long>(seq) * max_blocks;
 
-  if (tid < kRows) {
+  if (tid < kR) {
     row_m[tid] = -INFINITY;
     row_l[tid] = 0.f;
     row_c[tid] = 1.f;
     row_pos[tid] = tid < nrows ? positions[tok0 + tid / nh] : -1;
   }
   __syncthreads();
-  for (int r = warp; r < kRows; r += kTcWarps) {     // a warp per query row
+  for (int r = warp; r < kR; r += kWarps) {     // a warp per query row
     __nv_bfloat16* dst = Qs + r * Dp;
     if (r < nrows) {
       const int tok = tok0 + r / nh, h = h0 + r % nh;
@@ -337,7 +341,7 @@ latent_attention_tc_kernel(const TQ* __restrict__ ql, long long ql_st, long long
   const int vec_per_row = D >> 3;
   for (int j0 = k_begin; j0 < k_end; j0 += kTcKeys) {
     __syncthreads();
-    for (int jj = warp; jj < kTcKeys; jj += kTcWarps) {   // a warp per key row, asynchronous 16-byte copies
+    for (int jj = warp; jj < kTcKeys; jj += kWarps) {   // a warp per key row, asynchronous 16-byte copies
       const int j = j0 + jj;
       __nv_bfloat16* dst = Ks + jj * Dp;
       if (j < k_end) {
@@ -352,23 +356,33 @@ latent_attention_tc_kernel(const TQ* __restrict__ ql, long long ql_st, long long
     cp_async_wait_all();
     __syncthreads();
     {
-      float sacc[4] = {};
-      for (int k0 = 0; k0 < D; k0 += 16) {
+      float sacc[2][4] = {};                   // two independent accumulation chains over alternate k-steps
+      int k0 = 0;
+      for (; k0 + 32 <= D; k0 += 32) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          uint32_t a[4], b[2];
+          load_a_frag(a, Qs, Dp, 16 * wm, k0 + 16 * u, lane);
+          load_b_frag_nk(b, Ks, Dp, 8 * wn, k0 + 16 * u, lane);
+          mma_bf16_16816(sacc[u], a, b);
+        }
+      }
+      if (k0 < D) {
         uint32_t a[4], b[2];
-        load_a_frag(a, Qs, Dp, 0, k0, lane);
-        load_b_frag_nk(b, Ks, Dp, 8 * warp, k0, lane);
-        mma_bf16_16816(sacc, a, b);
+        load_a_frag(a, Qs, Dp, 16 * wm, k0, lane);
+        load_b_frag_nk(b, Ks, Dp, 8 * wn, k0, lane);
+        mma_bf16_16816(sacc[0], a, b);
       }
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const int r = g + (e >> 1) * 8, col = 8 * warp + 2 * t + (e & 1), j = j0 + col;
-        Ss[r * kSsLd + col] = (j < k_end && j <= row_pos[r]) ? sacc[e] * scale : -INFINITY;
+        const int r = 16 * wm + g + (e >> 1) * 8, col = 8 * wn + 2 * t + (e & 1), j = j0 + col;
+        Ss[r * kSsLd + col] = (j < k_end && j <= row_pos[r]) ? (sacc[0][e] + sacc[1][e]) * scale : -INFINITY;
       }
     }
     __syncthreads();
 #pragma unroll
-    for (int i = 0; i < kRows / kTcWarps; ++i) {
-      const int r = warp * (kRows / kTcWarps) + i;
+    for (int i = 0; i < kR / kWarps; ++i) {
+      const int r = warp * (kR / kWarps) + i;
       const float s0 = Ss[r * kSsLd + lane], s1 = Ss[r * kSsLd + lane + 32];
       const float m_old = row_m[r];
       const float m_new = fmaxf(m_old, warp_max(fmaxf(s0, s1)));
@@ -386,7 +400,7 @@ latent_attention_tc_kernel(const TQ* __restrict__ ql, long long ql_st, long long
     }
     __syncthreads();
     {
-      const float c_lo = row_c[g], c_hi = row_c[g + 8];
+      const float c_lo = row_c[16 * wm + g], c_hi = row_c[16 * wm + g + 8];
 #pragma unroll
       for (int i = 0; i < NT; ++i) {
         oacc[i][0] *= c_lo;
@@ -397,10 +411,10 @@ latent_attention_tc_kernel(const TQ* __restrict__ ql, long long ql_st, long long
 #pragma unroll
       for (int kk = 0; kk < kTcKeys / 16; ++kk) {
         uint32_t a[4];
-        load_a_frag(a, Ps, kPsLd, 0, 16 * kk, lane);
+        load_a_frag(a, Ps, kPsLd, 16 * wm, 16 * kk, lane);
 #pragma unroll
         for (int i = 0; i < NT; ++i) {
-          const int n0 = 8 * (warp * NT + i);
+          const int n0 = 8 * (wn * NT + i);
           if (n0 < R) {      // uniform over the warp
             uint32_t b[2];
             load_b_frag_kn(b, Ks, Dp, 16 * kk, n0, lane);
@@ -413,7 +427,7 @@ latent_attention_tc_kernel(const TQ* __restrict__ ql, long long ql_st, long long
   __syncthreads();
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
-    const int r = g + 8 * half;
+    const int r = 16 * wm + g + 8 * half;
     if (r >= nrows) continue;
     const int tok = tok0 + r / nh, h = h0 + r % nh;
     const long long base = static_cast<long long>(tok) * H + h;
@@ -421,7 +435,7 @@ latent_attention_tc_kernel(const TQ* __restrict__ ql, long long ql_st, long long
     float* dst = nsplit > 1 ? partial + (base * nsplit + split) * (R + 2) : nullptr;
 #pragma unroll
     for (int i = 0; i < NT; ++i) {
-      const int c = 8 * (warp * NT + i) + 2 * t;
+      const int c = 8 * (wn * NT + i) + 2 * t;
       if (c < R) {
         const float v0 = oacc[i][2 * half], v1 = oacc[i][2 * half + 1];
         if (dst) {
@@ -432,17 +446,20 @@ latent_attention_tc_kernel(const TQ* __restrict__ ql, long long ql_st, long long
         }
       }
     }
-    if (dst && warp == 0 && t == 0) {
+    if (dst && wn == 0 && t == 0) {
       dst[R] = row_m[r];
       dst[R + 1] = row_l[r];
     }
   }
 }
 
-static bool latent_attention_tc_ok(int R, int dr) {
+static size_t latent_attention_tc_smem(int R, int dr, int rows) {
+  return static_cast<size_t>(rows + kTcKeys) * (R + dr + 8) * 2 + static_cast<size_t>(rows) * (kSsLd * 4 + kPsLd * 2 + 16);
+}
+
+static bool latent_attention_tc_ok(int R, int dr, int rows = kRows) {
   const int D = R + dr;
-  const size_t smem = static_cast<size_t>(kRows + kTcKeys) * (D + 8) * 2 + kRows * kSsLd * 4 + kRows * kPsLd * 2 + 4 * kRows * 4;
-  return D % 16 == 0 && R % 8 == 0 && R <= 512 && smem <= 227 * 1024;
+  return D % 16 == 0 && R % 8 == 0 && R <= 512 && (rows == 16 || rows == 32) && latent_attention_tc_smem(R, dr, rows) <= 227 * 1024;
 }
 
 template <typename TQ>
@@ -450,24 +467,29 @@ static int launch_latent_attention_tc(const TQ* ql, long long ql_st, long long q
                                       const int* block_tables, int max_blocks, int block_size, const int* tiles, int ntiles,
                                       const int* positions, const float* freq, float mult, float scale, int H, int R, int dr,
                                       int heads_per_tile, int splits, int keys_per_split, void* out, float* partial,
-                                      int tokens, cudaStream_t s) {
-  const int D = R + dr;
-  const size_t smem = static_cast<size_t>(kRows + kTcKeys) * (D + 8) * 2 + kRows * kSsLd * 4 + kRows * kPsLd * 2 + 4 * kRows * 4;
-  const int nt = (R + 8 * kTcWarps - 1) / (8 * kTcWarps);
+                                      int tokens, int rows, cudaStream_t s) {
+  const size_t smem = latent_attention_tc_smem(R, dr, rows);
+  const int nt = (R + 63) / 64;
   dim3 grid(ntiles, (H + heads_per_tile - 1) / heads_per_tile, splits);
-#define LAUNCH_TC(NT)                                                                                                \
+#define LAUNCH_TC(NT, MT)                                                                                            \
   do {                                                                                                               \
-    auto kern = latent_attention_tc_kernel<NT, TQ>;                                                                    \
+    auto kern = latent_attention_tc_kernel<NT, MT, TQ>;                                                              \
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
     if (e != cudaSuccess) return static_cast<int>(e);                                                                \
-    kern<<<grid, kTcThreads, smem, s>>>(ql, ql_st, ql_sh, (const __nv_bfloat16*)q, ldq, dn, (const __nv_bfloat16*)cache, \
-                                          block_tables, max_blocks, block_size, tiles, positions, freq, mult, scale, \
-                                          H, R, dr, heads_per_tile, keys_per_split, (__nv_bfloat16*)out, partial);   \
+    kern<<<grid, 256 * MT, smem, s>>>(ql, ql_st, ql_sh, (const __nv_bfloat16*)q, ldq, dn, (const __nv_bfloat16*)cache, \
+                                      block_tables, max_blocks, block_size, tiles, positions, freq, mult, scale,     \
+                                      H, R, dr, heads_per_tile, keys_per_split, (__nv_bfloat16*)out, partial);       \
   } while (0)
-  if (nt <= 1) LAUNCH_TC(1);
-  else if (nt <= 2) LAUNCH_TC(2);
-  else if (nt <= 4) LAUNCH_TC(4);
-  else LAUNCH_TC(8);
+#define LAUNCH_TC_NT(MT)          \
+  do {                            \
+    if (nt <= 1) LAUNCH_TC(1, MT); \
+    else if (nt <= 2) LAUNCH_TC(2, MT); \
+    else if (nt <= 4) LAUNCH_TC(4, MT); \
+    else LAUNCH_TC(8, MT);        \
+  } while (0)
+  if (rows == 32) LAUNCH_TC_NT(2);
+  else LAUNCH_TC_NT(1);
+#undef LAUNCH_TC_NT
 #undef LAUNCH_TC
   if (splits > 1)
     latent_attention_merge_kernel<__nv_bfloat16><<<tokens * H, 128, 0, s>>>(partial, (__nv_bfloat16*)out, R, splits);
@@ -493,8 +515,8 @@ LLMCTL_API int llmctl_latent_kv_write(const void* d, long long ld, int Q, int R,
 // partial: fp32 scratch of tokens * H * splits * (R + 2) numbers when splits > 1 (may be null otherwise).
 // ql: absorbed queries, element (token, head, c) at ql[token * ql_st + head * ql_sh + c]; fp32, or bf16 (ql_bf16) on the
 // tensor-core path only (llmctl_latent_attention_uses_tensor_cores).
-LLMCTL_API int llmctl_latent_attention_uses_tensor_cores(int is_fp32, int R, int dr) {
-  return (!is_fp32 && latent_attention_tc_ok(R, dr)) ? 1 : 0;
+LLMCTL_API int llmctl_latent_attention_uses_tensor_cores(int is_fp32, int R, int dr, int rows_per_tile) {
+  return (!is_fp32 && latent_attention_tc_ok(R, dr, rows_per_tile)) ? 1 : 0;
 }
 
 LLMCTL_API int llmctl_latent_attention(const void* ql, int ql_bf16, long long ql_st, long long ql_sh, const void* q, long long ldq, int dn, const void* cache,
@@ -502,25 +524,25 @@ LLMCTL_API int llmctl_latent_attention(const void* ql, int ql_bf16, long long ql
                                        int ntiles, int tokens, const int* positions, const float* freq, float mult,
                                        float scale, int H, int R, int dr, int heads_per_tile, int splits,
                                        int keys_per_split, void* out, float* partial, int is_fp32, int tensor_cores,
-                                       void* stream) {
+                                       int rows_per_tile, void* stream) {
   LLMCTL_BEGIN();
   LLMCTL_REQUIRE(H > 0 && R > 0 && dr >= 0 && dr % 2 == 0 && block_size > 0 && heads_per_tile >= 1 &&
-                 heads_per_tile <= kRows && splits >= 1 && keys_per_split > 0 && (splits == 1 || partial != nullptr));
+                 heads_per_tile <= rows_per_tile && (rows_per_tile == 16 || rows_per_tile == 32) && splits >= 1 && keys_per_split > 0 && (splits == 1 || partial != nullptr));
   if (ntiles == 0) return 0;
   int rc;
-  if (!is_fp32 && tensor_cores && latent_attention_tc_ok(R, dr) && keys_per_split % kTcKeys == 0) {
+  if (!is_fp32 && tensor_cores && latent_attention_tc_ok(R, dr, rows_per_tile) && keys_per_split % kTcKeys == 0) {
     if (ql_bf16)
       rc = launch_latent_attention_tc<__nv_bfloat16>((const __nv_bfloat16*)ql, ql_st, ql_sh, q, ldq, dn, cache, block_tables, max_blocks,
                                                      block_size, tiles, ntiles, positions, freq, mult, scale, H, R, dr, heads_per_tile,
-                                                     splits, keys_per_split, out, partial, tokens, (cudaStream_t)stream);
+                                                     splits, keys_per_split, out, partial, tokens, rows_per_tile, (cudaStream_t)stream);
     else
     rc = launch_latent_attention_tc<float>((const float*)ql, ql_st, ql_sh, q, ldq, dn, cache, block_tables, max_blocks, block_size, tiles, ntiles, positions, freq,
                                     mult, scale, H, R, dr, heads_per_tile, splits, keys_per_split, out, partial, tokens,
-                                    (cudaStream_t)stream);
+                                    rows_per_tile, (cudaStream_t)stream);
     if (rc != 0) LLMCTL_FAIL(rc, "latent attention launch");
     LLMCTL_RETURN_LAST();
   }
-  LLMCTL_REQUIRE(!ql_bf16);
+  LLMCTL_REQUIRE(!ql_bf16 && rows_per_tile == kRows);
   LLMCTL_DISPATCH_DTYPE(is_fp32, T, (rc = launch_latent_attention<T>((const float*)ql, ql_st, ql_sh, q, ldq, dn, cache, block_tables, max_blocks, block_size,
                                                                      tiles, ntiles, positions, freq, mult, scale, H, R, dr,
                                                                      heads_per_tile, splits, keys_per_split, out, partial,

@@ -16,23 +16,22 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
-// A fragment of the 16 x 16 block at (row0, k0) of a row-major bf16 matrix in shared memory (ld in elements, even).
+// A fragment of the 16 x 16 block at (row0, k0) of a row-major bf16 matrix in shared memory: one ldmatrix.x4 (rows
+// must start on 16-byte boundaries: ld % 8 == 0, k0 % 8 == 0, 16-byte aligned base).
 __device__ __forceinline__ void load_a_frag(uint32_t (&a)[4], const __nv_bfloat16* m, int ld, int row0, int k0, int lane) {
-  const int g = lane >> 2, t = lane & 3;
-  const __nv_bfloat16* p = m + (row0 + g) * ld + k0 + 2 * t;
-  a[0] = *reinterpret_cast<const uint32_t*>(p);
-  a[1] = *reinterpret_cast<const uint32_t*>(p + 8 * ld);
-  a[2] = *reinterpret_cast<const uint32_t*>(p + 8);
-  a[3] = *reinterpret_cast<const uint32_t*>(p + 8 * ld + 8);
+  const __nv_bfloat16* p = m + (row0 + (lane & 15)) * ld + k0 + ((lane >> 4) << 3);
+  const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3])
+               : "r"(addr));
 }
 
 // B fragment when B[k][n] = m[n0 + n][k0 + k], i.e. the operand is stored [n][k] row-major (weights [out, in],
-// keys [key][dim]): both registers are contiguous pairs.
+// keys [key][dim]): one ldmatrix.x2 without transposition (same alignment rule).
 __device__ __forceinline__ void load_b_frag_nk(uint32_t (&b)[2], const __nv_bfloat16* m, int ld, int n0, int k0, int lane) {
-  const int g = lane >> 2, t = lane & 3;
-  const __nv_bfloat16* p = m + (n0 + g) * ld + k0 + 2 * t;
-  b[0] = *reinterpret_cast<const uint32_t*>(p);
-  b[1] = *reinterpret_cast<const uint32_t*>(p + 8);
+  const __nv_bfloat16* p = m + (n0 + (lane & 7)) * ld + k0 + (((lane >> 3) & 1) << 3);
+  const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(b[0]), "=r"(b[1]) : "r"(addr));
 }
 
 // B fragment when the operand is stored [k][n] row-major (values [key][dim]): ldmatrix with transposition.  Rows must

@@ -95,8 +95,9 @@ class LatentAttention(nn.Module):
         else:
             ql = torch.bmm(qn.float(), self.w_uk.float())
         ql = ql.transpose(0, 1)
-        ol = lops.latent_attention(ql, q, s.dim, cache, batch.block_tables, batch.tiles(s.heads), batch.positions,
-                                   self.rot_freq, self.rot_mult, s.scale, batch.heads_per_tile(s.heads), batch.max_context,
-                                   batch.attention_splits(s.heads))
+        rows = lops.rows_per_tile(q.dtype, s.kv_rank, s.rot_dim, q.is_cuda, s.heads if batch.decode_only else lops.ROWS_PER_TILE_WIDE)
+        ol = lops.latent_attention(ql, q, s.dim, cache, batch.block_tables, batch.tiles(rows), batch.positions,
+                                   self.rot_freq, self.rot_mult, s.scale, batch.heads_per_tile(s.heads, rows), batch.max_context,
+                                   batch.attention_splits(s.heads, rows), rows=rows)
         o = torch.bmm(ol.transpose(0, 1), self.w_uv.transpose(1, 2)).transpose(0, 1).reshape(T, s.heads * s.vdim)
         return ops.linear(o, self.w_o)

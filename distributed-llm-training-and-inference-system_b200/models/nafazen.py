@@ -36,6 +36,7 @@ from .mixers import LatentAttention, LatentAttentionSpec
 from .registry import Architecture, register_architecture
 
 MIXER_TYPES = ("latent_attention", "latent_attention_2")
+YARN_TYPES = ("latent_attention",)      # the second mixer type rotates with the plain frequencies
 
 
 @dataclass
@@ -70,7 +71,8 @@ class NafazenConfig:
             src = m.get("kv_from")
             spec = LatentAttentionSpec(heads=int(m["heads"]), dim=int(m["dim"]), rot_dim=int(m["rot_dim"]), vdim=int(m["vdim"]),
                                        kv_rank=int(m["kv_rank"]), q_rank=int(m["q_rank"]), scale=float(m["scale"]),
-                                       rot_base=float(rot["base"]), rot_scaling=rot.get("scaling") or None,
+                                       rot_base=float(rot["base"]),
+                                       rot_scaling=(rot.get("scaling") or None) if l["type"] in YARN_TYPES else None,
                                        kv_from=None if src is None else int(src))
             if src is not None:
                 if not 0 <= int(src) < i or layers[int(src)].mixer.kv_from is not None:
@@ -141,12 +143,12 @@ class NafazenModel(nn.Module):
         with torch.no_grad():
             self.embed.copy_(get("embed"))
             self.head.copy_(get("head"))
-            self.final_norm.copy_(get("final.norm").float())
+            self.final_norm.copy_(get("final.norm").float().reshape(()))
             for i, blk in enumerate(self.blocks):
-                blk.norm1.copy_(get(f"l{i}.norm1").float())
+                blk.norm1.copy_(get(f"l{i}.norm1").float().reshape(()))
                 blk.mixer.load(get, f"l{i}.mix.")
                 if blk.mlp is not None:
-                    blk.norm2.copy_(get(f"l{i}.norm2").float())
+                    blk.norm2.copy_(get(f"l{i}.norm2").float().reshape(()))
                     blk.mlp.load(get, f"l{i}.mlp.")
 
     def init_random(self, seed: int = 0, std: float = 0.02) -> None:

@@ -20,16 +20,27 @@ native.register_signature("llmctl_latent_kv_write", [c_void_p, c_ll, c_int, c_in
                                                       c_void_p, c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_void_p])
 native.register_signature("llmctl_latent_attention", [c_void_p, c_int, c_ll, c_ll, c_void_p, c_ll, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p,
                                                        c_int, c_int, c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_int,
-                                                       c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p])
+                                                       c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
 native._KERNELS_PER_CALL["llmctl_latent_attention"] = 1
 
 ROWS_PER_TILE = 16          # query rows (token, head) a CTA owns; tiles are built by the engine with this limit
+ROWS_PER_TILE_WIDE = 32     # the tensor-core kernel also takes tiles of 32 rows (half the key traffic per row)
 
 
 def uses_tensor_cores(dtype: torch.dtype, R: int, dr: int) -> bool:
     """bf16 with these sizes runs the mma.sync kernel (which also takes bf16 absorbed queries); same rule as
     llmctl_latent_attention_uses_tensor_cores."""
     return dtype == torch.bfloat16 and (R + dr) % 16 == 0 and R % 8 == 0 and R <= 512
+
+
+def rows_per_tile(dtype: torch.dtype, R: int, dr: int, cuda: bool, rows_wanted: int = ROWS_PER_TILE_WIDE) -> int:
+    """Query rows per attention tile for these sizes: 32 where the tensor-core kernel runs, its shared memory
+    ((rows + 64 keys) x (R + dr + 8) bf16 + score and probability tiles) fits and a tile has more than 16 rows to fill
+    (``rows_wanted``: the tokens of a prompt portion, or the heads of a decoding token), else 16."""
+    wide = ROWS_PER_TILE_WIDE
+    smem = (wide + 64) * (R + dr + 8) * 2 + wide * (68 * 4 + 72 * 2 + 16)
+    ok = cuda and rows_wanted > ROWS_PER_TILE and uses_tensor_cores(dtype, R, dr) and smem <= 227 * 1024
+    return wide if ok else ROWS_PER_TILE
 
 
 def latent_kv_write(d: torch.Tensor, Q: int, R: int, dr: int, wq: torch.Tensor, wkv: Optional[torch.Tensor],
@@ -60,10 +71,11 @@ def latent_kv_write(d: torch.Tensor, Q: int, R: int, dr: int, wq: torch.Tensor, 
 
 def latent_attention(ql: torch.Tensor, q: torch.Tensor, dn: int, cache: torch.Tensor, block_tables: torch.Tensor,
                      tiles: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor, mult: float, scale: float,
-                     heads_per_tile: int, max_context: int, splits: int = 1, tensor_cores: bool = True) -> torch.Tensor:
+                     heads_per_tile: int, max_context: int, splits: int = 1, tensor_cores: bool = True,
+                     rows: int = ROWS_PER_TILE) -> torch.Tensor:
     """ql: [T, H, R] absorbed queries (any token / head strides; fp32, or bf16 where ``uses_tensor_cores``); q: [T, H * (dn + dr)] raw queries (the rope part of each head is rotated
     here); tiles: int32 [n, 4] = (first token row, tokens, block-table row, 0) with tokens * heads_per_tile <=
-    ROWS_PER_TILE, all tokens of a tile in one sequence with growing positions.  Returns [T, H, R] in q's type:
+    ``rows`` (16, or 32 where ``rows_per_tile`` says so), all tokens of a tile in one sequence with growing positions.  Returns [T, H, R] in q's type:
     softmax(scale * (ql . c + rot(qr) . kr)) c over cache positions 0..position of each token."""
     T, H, R = ql.shape
     D = cache.shape[-1]
@@ -81,7 +93,7 @@ def latent_attention(ql: torch.Tensor, q: torch.Tensor, dn: int, cache: torch.Te
                     q.data_ptr(), q.stride(0), dn, cache.data_ptr(),
                     block_tables.data_ptr(), block_tables.shape[1], block_size, tiles.data_ptr(), tiles.shape[0], T,
                     positions.data_ptr(), freq.data_ptr(), float(mult), float(scale), H, R, dr, heads_per_tile, splits, per,
-                    out.data_ptr(), native.ptr(partial), _is32(q), int(tensor_cores), native.stream_ptr())
+                    out.data_ptr(), native.ptr(partial), _is32(q), int(tensor_cores), int(rows), native.stream_ptr())
         return out
     out = torch.zeros(T, H, R, dtype=torch.float32)
     rows = cache.view(-1, D).float()

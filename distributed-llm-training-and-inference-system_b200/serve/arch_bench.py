@@ -100,11 +100,14 @@ def _kernels(size: Dict[str, Any], peaks: Dict[str, float]) -> Dict[str, Any]:
         T = b.num_tokens
         ql = torch.randn(T, H, R, device=dev)
         q = torch.randn(T, H * (dn + dr), device=dev).to(torch.bfloat16)
-        t = _time(lambda: L.latent_attention(ql, q, dn, cache, b.block_tables, b.tiles(H), b.positions, freq, mult, 0.07,
-                                             b.heads_per_tile(H), b.max_context, b.attention_splits(H)), 5)
+        rows = L.rows_per_tile(q.dtype, R, dr, True, H if new == 1 else 32)                     # the tiling and query type the model path takes
+        if L.uses_tensor_cores(q.dtype, R, dr):
+            ql = ql.to(torch.bfloat16)
+        t = _time(lambda: L.latent_attention(ql, q, dn, cache, b.block_tables, b.tiles(rows), b.positions, freq, mult, 0.07,
+                                             b.heads_per_tile(H, rows), b.max_context, b.attention_splits(H, rows), rows=rows), 5)
         keys = nseq * (ctx * new - new * (new - 1) // 2)                 # visible (query, key) pairs per head
         flops = 2.0 * H * keys * (2 * R + dr)
-        bytes_ = nseq * ctx * (R + dr) * 2 + T * H * (R * 4 + R * 2)
+        bytes_ = nseq * ctx * (R + dr) * 2 + T * H * (R * ql.element_size() + R * 2)
         res[f"latent_attention_{name}"] = {"ms": t * 1e3, "tflops": flops / t / 1e12, "gbs": bytes_ / t / 1e9,
                                            "frac_of_bf16_peak": flops / t / 1e12 / peaks["bf16_tflops"],
                                            "frac_of_hbm": bytes_ / t / 1e9 / peaks["hbm_gbs"]}
@@ -117,7 +120,41 @@ def _kernels(size: Dict[str, Any], peaks: Dict[str, float]) -> Dict[str, Any]:
     t = _time(lambda: M.moe_ffn(x, torch.bfloat16, wr, wgu, wd, top, scale_input=True), 5)
     flops = 2.0 * T * top * 3 * F * W
     res["moe_ffn_4096_tokens"] = {"ms": t * 1e3, "tflops": flops / t / 1e12, "frac_of_bf16_peak": flops / t / 1e12 / peaks["bf16_tflops"]}
+    res.update(_gpt_kernels(size, peaks))
     res["native_launches"] = native.launch_count
+    return res
+
+
+def _gpt_kernels(size: Dict[str, Any], peaks: Dict[str, float]) -> Dict[str, Any]:
+    """The GPT family's like kernels at like sizes: causal flash attention over the same 2 x 2048 tokens, paged decode
+    attention over the same 32 contexts of 4096 (head size 128 for both), and the SwiGLU feed-forward's two GEMMs on
+    4096 tokens at the width that gives the mixture-of-experts layer's active parameters."""
+    from ..ops import functional as ops
+    from ..ops import serving as S
+    dev = torch.device("cuda")
+    H, D, res = size["heads"], 128, {}
+    B, n = 2, 2048
+    q, k, v = (torch.randn(B, n, H, D, device=dev).to(torch.bfloat16) for _ in range(3))
+    t = _time(lambda: ops.attention(q, k, v, causal=True), 5)
+    flops = 4.0 * B * H * D * n * (n + 1) / 2
+    res["gpt_flash_attention_prefill"] = {"ms": t * 1e3, "tflops": flops / t / 1e12, "frac_of_bf16_peak": flops / t / 1e12 / peaks["bf16_tflops"]}
+    nseq, ctx, bs = 32, 4096, 64
+    per = ctx // bs
+    kc, vc = (torch.randn(nseq * per, bs, H, D, device=dev).to(torch.bfloat16) for _ in range(2))
+    tables = torch.arange(nseq * per, dtype=torch.int32, device=dev).view(nseq, per)
+    lens = torch.full((nseq,), ctx, dtype=torch.int32, device=dev)
+    qd = torch.randn(nseq, H, D, device=dev).to(torch.bfloat16)
+    t = _time(lambda: S.paged_attention_decode(qd, kc, vc, tables, lens, ctx), 5)
+    bytes_ = 2.0 * nseq * ctx * H * D * 2
+    res["gpt_paged_attention_decode"] = {"ms": t * 1e3, "gbs": bytes_ / t / 1e9, "frac_of_hbm": bytes_ / t / 1e9 / peaks["hbm_gbs"]}
+    W, T = size["width"], 4096
+    F = size["top"] * size["expert_ff"]
+    x = torch.randn(T, W, device=dev).to(torch.bfloat16)
+    wgu = (torch.randn(2 * F, W, device=dev) / W ** 0.5).to(torch.bfloat16)
+    wd = (torch.randn(W, F, device=dev) / F ** 0.5).to(torch.bfloat16)
+    t = _time(lambda: ops.linear(ops.swiglu(ops.linear(x, wgu)), wd), 5)
+    flops = 2.0 * T * 3 * F * W
+    res["gpt_swiglu_ffn_4096_tokens"] = {"ms": t * 1e3, "tflops": flops / t / 1e12, "frac_of_bf16_peak": flops / t / 1e12 / peaks["bf16_tflops"]}
     return res
 
 

@@ -13,7 +13,7 @@ from typing import List, Optional, Sequence as Seq, Tuple
 import numpy as np
 import torch
 
-from ..ops.latent_attention import ROWS_PER_TILE
+from ..ops.latent_attention import ROWS_PER_TILE, ROWS_PER_TILE_WIDE
 
 
 @dataclass
@@ -37,10 +37,12 @@ class RaggedBatch:
                  pad_to: Optional[Tuple[int, int, int]] = None):
         self.block_size, self.device, self._sms, self.pad_to = block_size, device, sm_count, pad_to
         self.decode_only = all(len(p.tokens) == 1 for p in portions)
-        self.tokens_per_tile = 1 if self.decode_only else ROWS_PER_TILE
+        # attention query tiles come in two widths: 16 rows, and 32 rows for kernels that take them
+        self._tile_tokens = (1, 1) if self.decode_only else (ROWS_PER_TILE, ROWS_PER_TILE_WIDE)
         if pad_to is not None:
             assert self.decode_only and len(portions) <= pad_to[0]
-            T = B = n_out = ntiles = pad_to[0]
+            T = B = n_out = pad_to[0]
+            ntiles = (T, T)
             max_blocks, self.max_context = pad_to[1], pad_to[2]
         else:
             T = sum(len(p.tokens) for p in portions)
@@ -49,23 +51,24 @@ class RaggedBatch:
             self.max_context = max(p.start + len(p.tokens) for p in portions)
             max_blocks = max(len(p.block_table) for p in portions)
             n_out = sum(len(p.want) for p in portions)
-            ntiles = sum((len(p.tokens) + self.tokens_per_tile - 1) // self.tokens_per_tile for p in portions)
-        # int32 words: tokens(2T) | slots(2T) | out_rows(2 n_out) | positions(T) | tiles(4 ntiles) | block tables(B max_blocks)
-        sizes = [2 * T, 2 * T, 2 * n_out, T, 4 * ntiles, B * max_blocks]
+            ntiles = tuple(sum((len(p.tokens) + w - 1) // w for p in portions) for w in self._tile_tokens)
+        # int32 words: tokens(2T) | slots(2T) | out_rows(2 n_out) | positions(T) | tiles(4 n16) | block tables(B max_blocks) | wide tiles(4 n32)
+        sizes = [2 * T, 2 * T, 2 * n_out, T, 4 * ntiles[0], B * max_blocks, 4 * ntiles[1]]
         offs = np.concatenate([[0], np.cumsum(sizes)])
         self._host = torch.zeros(int(offs[-1]), dtype=torch.int32, pin_memory=device.type == "cuda")
         a = self._host.numpy()
         self._h = (a[offs[0]:offs[1]].view(np.int64), a[offs[1]:offs[2]].view(np.int64), a[offs[2]:offs[3]].view(np.int64),
-                   a[offs[3]:offs[4]], a[offs[4]:offs[5]].reshape(ntiles, 4), a[offs[5]:offs[6]].reshape(B, max_blocks))
+                   a[offs[3]:offs[4]], (a[offs[4]:offs[5]].reshape(ntiles[0], 4), a[offs[6]:offs[7]].reshape(ntiles[1], 4)),
+                   a[offs[5]:offs[6]].reshape(B, max_blocks))
         dev = torch.empty_like(self._host, device=device) if device.type == "cuda" else self._host
         self._dev = dev
         self.nbytes = self._host.numel() * 4
-        self.num_tokens, self.num_out, self.num_tiles = T, n_out, ntiles
+        self.num_tokens, self.num_out, self.num_tiles = T, n_out, ntiles[0]
         self.tokens = dev[offs[0]:offs[1]].view(torch.int64)
         self.slots = dev[offs[1]:offs[2]].view(torch.int64)
         self.out_rows = dev[offs[2]:offs[3]].view(torch.int64)
         self.positions = dev[offs[3]:offs[4]]
-        self._tiles = dev[offs[4]:offs[5]].view(ntiles, 4)
+        self._tiles = {ROWS_PER_TILE: dev[offs[4]:offs[5]].view(ntiles[0], 4), ROWS_PER_TILE_WIDE: dev[offs[6]:offs[7]].view(ntiles[1], 4)}
         self.block_tables = dev[offs[5]:offs[6]].view(B, max_blocks)
         self.refill(portions)
 
@@ -80,9 +83,10 @@ class RaggedBatch:
             positions[:] = 0
             tables[:] = 0
             for r in range(self.pad_to[0]):                 # padding rows too: one tile and one (ignored) logits row each
-                tiles[r] = (r, 1, r, 0)
+                tiles[0][r] = tiles[1][r] = (r, 1, r, 0)
                 out_rows[r] = r
-        t = o = ti = 0
+        t = o = 0
+        ti = [0, 0]
         for b, p in enumerate(portions):
             n = len(p.tokens)
             bt = np.asarray(p.block_table, dtype=np.int64)
@@ -98,24 +102,26 @@ class RaggedBatch:
                     assert 0 <= w < n
                     out_rows[o] = t + w
                     o += 1
-                for s in range(0, n, self.tokens_per_tile):
-                    tiles[ti] = (t + s, min(self.tokens_per_tile, n - s), b, 0)
-                    ti += 1
+                for k, width in enumerate(self._tile_tokens):
+                    for s in range(0, n, width):
+                        tiles[k][ti[k]] = (t + s, min(width, n - s), b, 0)
+                        ti[k] += 1
             t += n
         if self._dev is not self._host:
             self._dev.copy_(self._host, non_blocking=True)
 
     # ---- attention tiling -----------------------------------------------------------------------------------
-    def tiles(self, heads: int) -> torch.Tensor:
-        return self._tiles
+    def tiles(self, rows: int = ROWS_PER_TILE) -> torch.Tensor:
+        """int32 [n, 4] = (first token row, tokens, block-table row, 0) for kernels whose CTAs own ``rows`` query rows."""
+        return self._tiles[rows]
 
-    def heads_per_tile(self, heads: int) -> int:
-        """A tile holds ROWS_PER_TILE (token, head) rows: 16 tokens x 1 head in a batch with prompt portions, 1 token x up
-        to 16 heads when every sequence decodes."""
-        return min(heads, ROWS_PER_TILE) if self.decode_only else 1
+    def heads_per_tile(self, heads: int, rows: int = ROWS_PER_TILE) -> int:
+        """A tile holds ``rows`` (token, head) rows: ``rows`` tokens x 1 head in a batch with prompt portions, 1 token x
+        up to ``rows`` heads when every sequence decodes."""
+        return min(heads, rows) if self.decode_only else 1
 
-    def attention_splits(self, heads: int) -> int:
+    def attention_splits(self, heads: int, rows: int = ROWS_PER_TILE) -> int:
         """Split the keys of long contexts over CTAs when the tiles alone would leave most SMs idle."""
-        hpt = self.heads_per_tile(heads)
-        ctas = self.num_tiles * ((heads + hpt - 1) // hpt)
+        hpt = self.heads_per_tile(heads, rows)
+        ctas = self._tiles[rows].shape[0] * ((heads + hpt - 1) // hpt)
         return int(max(1, min(2 * self._sms // max(ctas, 1), self.max_context // 64)))

@@ -21,9 +21,16 @@ def make_engine(cfg, weights, dt=torch.float32, device="cpu", blocks=16, bs=8, m
     return eng
 
 
-def small_cfg(**kw):
+def small_cfg(per_layer=None, **kw):
+    """``per_layer``: {layer index: mixer keys to override}, so that layers of one model differ in their sizes."""
     from llmctl_b200.models.nafazen import example_config
-    return example_config(**kw)
+    cfg = example_config(**kw)
+    for i, over in (per_layer or {}).items():
+        m = cfg["layers"][i]["mixer"]
+        m.update(over)
+        if "rot_dim" in over:
+            m["rot"]["dims"] = over["rot_dim"]
+    return cfg
 
 
 def run_cut(eng, sid, toks, cuts):
@@ -148,6 +155,11 @@ CONFIGS = {
     # sizes that the usual example makes equal, or 1: one head, top 1, latent wider than the model, no shared expert
     "odd": dict(width=40, heads=1, dim=6, rot_dim=2, vdim=10, kv_rank=48, q_rank=5, ff=20, experts=3, top=1, expert_ff=8,
                 shared_ff=None, pattern="bMcDa-", softcap=None, embedding_scale=0.5),
+    # every layer with sizes of its own; the layer that reads another's cache shares only its latent and rope sizes
+    "per_layer": dict(width=56, heads=3, dim=8, rot_dim=4, vdim=6, kv_rank=24, q_rank=10, pattern="aDbMcDaMc-", top=2, experts=5,
+                      per_layer={0: dict(heads=4, rot_dim=8, scale=0.31), 1: dict(heads=2, dim=6, kv_rank=16, rot_dim=6, q_rank=20),
+                                 2: dict(heads=5, dim=4, vdim=9, kv_rank=16, rot_dim=6, q_rank=7, scale=0.2),
+                                 4: dict(heads=1, dim=10, vdim=3, kv_rank=16, rot_dim=6, q_rank=33)}),
     "many_heads": dict(width=48, heads=5, dim=4, rot_dim=6, vdim=3, kv_rank=9, q_rank=16, experts=6, top=3, pattern="aMbDcMcD", yarn=False),
 }
 
@@ -246,7 +258,7 @@ def test_far_key_is_found_across_pages():
         ql[0, :, 0] = 9.0
         q = torch.zeros(1, H * (dn + dr))
         b = RaggedBatch([Portion(1, [0], n - 1, [], table)], bs, torch.device("cpu"))
-        out = L.latent_attention(ql, q, dn, cache, b.block_tables, b.tiles(H), b.positions, f, 1.0, 1.0, b.heads_per_tile(H), n)
+        out = L.latent_attention(ql, q, dn, cache, b.block_tables, b.tiles(), b.positions, f, 1.0, 1.0, b.heads_per_tile(H), n)
         assert torch.allclose(out[0, 0], r[far, :R], atol=1e-3), f"far key at {far}"
 
 

@@ -89,10 +89,17 @@ def test_latent_attention_kernels(cuda_device, dt, H, dn, dr, R, Q, bs):
             q = torch.randn(T, H * (dn + dr), generator=g).to(dt).to(dev)
             ql = torch.randn(T, H, R, generator=g).to(dev)
             cq = L.latent_kv_write(d, Q, R, dr, wq.to(dev), wkv.to(dev), cch, b.slots, b.positions, freq.to(dev), mult, 1e-5)
-            out = L.latent_attention(ql, q, dn, cch, b.block_tables, b.tiles(H), b.positions, freq.to(dev), mult, 0.3,
+            out = L.latent_attention(ql, q, dn, cch, b.block_tables, b.tiles(), b.positions, freq.to(dev), mult, 0.3,
                                      b.heads_per_tile(H), b.max_context, b.attention_splits(H) if rnd == 0 else 2)
             if dev == "cpu":
                 ref = (cq, out)
+            else:
+                rows = L.rows_per_tile(dt, R, dr, True)
+                if rows != L.ROWS_PER_TILE:          # the wide tiles the model path takes for these sizes
+                    wide = L.latent_attention(ql.to(dt), q, dn, cch, b.block_tables, b.tiles(rows), b.positions, freq.to(dev), mult,
+                                              0.3, b.heads_per_tile(H, rows), b.max_context,
+                                              b.attention_splits(H, rows) if rnd == 0 else 3, rows=rows)
+                    close(wide, ref[1], dt, 4)
         close(cq, ref[0], dt, 4)
         close(out, ref[1], dt, 4)
     close(cache_g, cache, dt, 4)
