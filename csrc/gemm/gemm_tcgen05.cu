@@ -45,7 +45,18 @@ struct GemmGate {
   long long b_slab;          // elements per flag
   long long b_row_stride;    // K-major B: elements between consecutive N rows
   long long b_span;          // MN-major B: elements of the whole matrix (a tile touches every K row)
+  // Grouped GEMM (mixture of experts): B is [experts * N, K] (K-major) and tile-row block i of A multiplies the matrix of
+  // expert grp_tile_expert[i]; blocks at and beyond *grp_num_tiles (a device-side count) are skipped by every role.
+  const int* grp_tile_expert;
+  const int* grp_num_tiles;
+  int grp_experts;
 };
+// Row of B where the tile's N range starts, or -1 if this tile-row block holds no rows (grouped mode only).
+__device__ __forceinline__ int grouped_b_row(const GemmGate& g, int m_blk, int n0, int N) {
+  if (g.grp_tile_expert == nullptr) return n0;
+  if (m_blk >= *g.grp_num_tiles) return -1;
+  return g.grp_tile_expert[m_blk] * N + n0;
+}
 __device__ __forceinline__ int gate_perm(const GemmGate& g, int i) {
   if (!g.perm) return i;
   if (i < g.bpc) return g.rank * g.bpc + i;
@@ -163,6 +174,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         mb_ = gate_perm(gate, mb_);
         const int m0 = mb_ * kBM;
         const int n0 = nb_ * BN;
+        const int b_row = grouped_b_row(gate, mb_, n0, N);
+        if (b_row < 0) continue;
         gate_wait(gate, m0, min(m0 + kBM, M));
         gate_wait_b<B_MN>(gate, n0, min(n0 + BN, N));
         for (int kb = 0; kb < num_kb; ++kb) {
@@ -179,7 +192,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               tma_load_2d(sA + g * 8192, &tmA, &bar_full[stage], m0 + g * 64, k0);
           }
           if (!B_MN) {
-            tma_load_2d(sB, &tmB, &bar_full[stage], k0, n0);
+            tma_load_2d(sB, &tmB, &bar_full[stage], k0, b_row);
           } else {
 #pragma unroll
             for (int g = 0; g < BN / 64; ++g)
@@ -201,6 +214,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       int acc = 0;
       uint32_t aphase = 0;
       for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+        if (gate.grp_tile_expert != nullptr) {
+          int mb_, nb_;
+          tile_to_mn(tile, num_m, num_n, mb_, nb_);
+          if (grouped_b_row(gate, mb_, 0, N) < 0) continue;
+        }
         mbar_wait(&bar_tempty[acc], aphase ^ 1u);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
@@ -239,6 +257,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       mb_ = gate_perm(gate, mb_);
       const int m0 = mb_ * kBM;
       const int n0 = nb_ * BN;
+      if (grouped_b_row(gate, mb_, n0, N) < 0) continue;
       mbar_wait(&bar_tfull[acc], aphase);
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
@@ -556,7 +575,7 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   if (!A_MN) rc = get_tmap_2d_bf16(&tmA, A, M, K, lda, kBM, kBK, 1);
   else rc = get_tmap_2d_bf16(&tmA, A, K, M, lda, kBK, 64, 1);
   if (rc) LLMCTL_FAIL(rc, "tensor map A");
-  if (!B_MN) rc = get_tmap_2d_bf16(&tmB, B, N, K, ldb, BN, kBK, 1);
+  if (!B_MN) rc = get_tmap_2d_bf16(&tmB, B, static_cast<uint64_t>(N) * (gate.grp_tile_expert ? gate.grp_experts : 1), K, ldb, BN, kBK, 1);
   else rc = get_tmap_2d_bf16(&tmB, B, K, N, ldb, kBK, 64, 1);
   if (rc) LLMCTL_FAIL(rc, "tensor map B");
   auto kern = gemm_tcgen05_kernel<BN, A_MN, B_MN, OutT>;
@@ -681,6 +700,22 @@ LLMCTL_API int llmctl_gemm_bf16(const void* A, const void* B, void* C, int M, in
                                 int out_fp32, int beta, int tile_n, int max_ctas, void* stream) {
   return gemm_bf16_impl(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_fp32, beta, tile_n, max_ctas, stream,
                         GemmGate{});
+}
+
+// Grouped GEMM for mixture-of-experts layers: C[r, :] = A[r, :] W[expert(r)]^T over `max_tiles` blocks of 128 rows of A
+// ([max_tiles * 128, K], K-major); W: [experts, N, K] contiguous; tile_expert[i] names the expert of row block i and
+// *num_tiles (on the device) says how many leading blocks hold rows — the others are skipped, their rows of C stay
+// unwritten.  One persistent launch for all experts; no host synchronisation.
+LLMCTL_API int llmctl_gemm_bf16_grouped(const void* A, const void* W, void* C, int max_tiles, int N, int K, long long lda,
+                                        long long ldc, const int* tile_expert, const int* num_tiles, int experts,
+                                        void* stream) {
+  LLMCTL_REQUIRE(tile_expert != nullptr && num_tiles != nullptr && experts >= 1 && max_tiles >= 1 && K % 8 == 0 &&
+                 static_cast<long long>(max_tiles) * kBM < (1LL << 31) && static_cast<long long>(experts) * N < (1LL << 31));
+  GemmGate g{};
+  g.grp_tile_expert = tile_expert;
+  g.grp_num_tiles = num_tiles;
+  g.grp_experts = experts;
+  return gemm_bf16_impl(A, W, C, max_tiles * kBM, N, K, lda, K, ldc, 0, 0, 0, 0, N > 128 ? 256 : 128, 0, stream, g);
 }
 
 LLMCTL_SYMM_WATCHDOG_MODULE(gemm)

@@ -14,6 +14,8 @@
 //                        of one expert (row tiles never straddle experts thanks to the padding).  bf16 with K and N
 //                        multiples of 8 runs 64 x 128 tiles on the tensor cores (mma.sync m16n8k16, fp32 accumulation,
 //                        next k-slice prefetched into registers); fp32 and odd sizes run the FMA kernel.
+//                        bf16 on 128-row tiles can instead run on the tcgen05 GEMM's grouped mode (llmctl_gemm_bf16_grouped,
+//                        csrc/gemm/gemm_tcgen05.cu), which reads the same plan.
 //   llmctl_moe_combine : y[t] = sum_k (w_k if the weight applies to the OUTPUT) * expert_out[row(t, k)]
 //                               + gate[t] * shared_out[t], in a fixed order (deterministic), fp32.
 // Reference: none (the reference has no model code).
@@ -75,7 +77,7 @@ moe_route_kernel(const float* __restrict__ x, const T* __restrict__ wr, const T*
 }
 
 // meta: int32 [2 * E + 2 + max_tiles] = { offsets[E] | cursor[E] | num_tiles | padded rows | tile_expert[max_tiles] }
-__global__ void moe_plan_kernel(const int* __restrict__ counts, int E, int* __restrict__ meta, int max_tiles) {
+__global__ void moe_plan_kernel(const int* __restrict__ counts, int E, int* __restrict__ meta, int max_tiles, int tile_m) {
   if (threadIdx.x != 0) return;
   int* offsets = meta;
   int* cursor = meta + E;
@@ -84,9 +86,9 @@ __global__ void moe_plan_kernel(const int* __restrict__ counts, int E, int* __re
   for (int e = 0; e < E; ++e) {
     offsets[e] = row;
     cursor[e] = 0;
-    const int nt = (counts[e] + kTileM - 1) / kTileM;
+    const int nt = (counts[e] + tile_m - 1) / tile_m;
     for (int i = 0; i < nt && tile < max_tiles; ++i) tile_expert[tile++] = e;
-    row += nt * kTileM;
+    row += nt * tile_m;
   }
   meta[2 * E] = tile;
   meta[2 * E + 1] = row;
@@ -262,9 +264,12 @@ LLMCTL_API int llmctl_moe_route(const float* x, const void* wr, const void* wg, 
   LLMCTL_RETURN_LAST();
 }
 
-LLMCTL_API int llmctl_moe_plan(const int* counts, int E, int* meta, int max_tiles, void* stream) {
+// tile_rows: the row tile of the grouped GEMM that will read the plan: llmctl_moe_tile_rows() for llmctl_grouped_gemm,
+// 128 for llmctl_gemm_bf16_grouped (which takes tile_expert = meta + 2 E + 2 and num_tiles = meta + 2 E).
+LLMCTL_API int llmctl_moe_plan(const int* counts, int E, int* meta, int max_tiles, int tile_rows, void* stream) {
   LLMCTL_BEGIN();
-  moe_plan_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(counts, E, meta, max_tiles);
+  LLMCTL_REQUIRE(tile_rows == kTileM || tile_rows == 128);
+  moe_plan_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(counts, E, meta, max_tiles, tile_rows);
   LLMCTL_RETURN_LAST();
 }
 

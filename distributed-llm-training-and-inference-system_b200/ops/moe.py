@@ -17,7 +17,9 @@ from .elementwise import _is32, gated_silu
 c_void_p, c_int, c_ll, c_float = native.c_void_p, native.c_int, native.c_ll, native.c_float
 native.register_signature("llmctl_moe_route", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                                 c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
-native.register_signature("llmctl_moe_plan", [c_void_p, c_int, c_void_p, c_int, c_void_p])
+native.register_signature("llmctl_moe_plan", [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p])
+native.register_signature("llmctl_gemm_bf16_grouped", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_ll, c_ll, c_void_p, c_void_p,
+                                                        c_int, c_void_p])
 native.register_signature("llmctl_moe_permute", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                                   c_int, c_int, c_int, c_void_p])
 native.register_signature("llmctl_grouped_gemm", [c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_int, c_int, c_void_p, c_int, c_int,
@@ -25,6 +27,12 @@ native.register_signature("llmctl_grouped_gemm", [c_void_p, c_ll, c_void_p, c_vo
 native.register_signature("llmctl_moe_combine", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                                   c_int, c_int, c_void_p])
 TILE_ROWS = 64      # row tile of the grouped GEMM (llmctl_moe_tile_rows)
+TILE_ROWS_TCGEN05 = 128     # row tile of the tcgen05 GEMM's grouped mode
+
+
+def uses_tcgen05(act_dtype: torch.dtype, W: int, F: int) -> bool:
+    """bf16 expert GEMMs whose rows are TMA-addressable (16-byte row pitch) run on the tcgen05 GEMM's grouped mode."""
+    return (act_dtype == torch.bfloat16 and W % 8 == 0 and F % 8 == 0 and native.has_symbol("llmctl_gemm_bf16_grouped"))
 
 
 def route(x: torch.Tensor, w_router: torch.Tensor, top: int, w_gate: Optional[torch.Tensor] = None, softmax: bool = False,
@@ -63,21 +71,32 @@ def moe_ffn(x: torch.Tensor, act_dtype: torch.dtype, w_router: torch.Tensor, w_g
     if x.is_cuda:
         is32 = int(act_dtype == torch.float32)
         pairs = T * top
-        max_tiles = (pairs + TILE_ROWS - 1) // TILE_ROWS + E
+        F_ = F2 // 2
+        tc5 = uses_tcgen05(act_dtype, W, F_) and w_gate_up.dtype == torch.bfloat16 and w_gate_up.is_contiguous() and w_down.is_contiguous()
+        rows = TILE_ROWS_TCGEN05 if tc5 else TILE_ROWS
+        max_tiles = (pairs + rows - 1) // rows + min(E, pairs)      # every expert's segment is padded to whole tiles
         meta = torch.empty(2 * E + 2 + max_tiles, dtype=torch.int32, device=x.device)
         pair_row = torch.empty(pairs, dtype=torch.int32, device=x.device)
-        xs = torch.empty(max_tiles * TILE_ROWS, W, dtype=act_dtype, device=x.device)
+        xs = torch.empty(max_tiles * rows, W, dtype=act_dtype, device=x.device)
         st = native.stream_ptr()
-        native.call("llmctl_moe_plan", counts.data_ptr(), E, meta.data_ptr(), max_tiles, st)
+        native.call("llmctl_moe_plan", counts.data_ptr(), E, meta.data_ptr(), max_tiles, rows, st)
         native.call("llmctl_moe_permute", x.data_ptr(), W, ids.data_ptr(), wts.data_ptr(), int(scale_input), meta.data_ptr(), E,
                     pair_row.data_ptr(), xs.data_ptr(), is32, T, top, st)
-        gu = torch.empty(max_tiles * TILE_ROWS, F2, dtype=act_dtype, device=x.device)
-        native.call("llmctl_grouped_gemm", xs.data_ptr(), W, w_gate_up.data_ptr(), gu.data_ptr(), F2, F2, W, meta.data_ptr(), E,
-                    max_tiles, is32, st)
-        act = gated_silu(gu)
-        eo = torch.empty(max_tiles * TILE_ROWS, W, dtype=act_dtype, device=x.device)
-        native.call("llmctl_grouped_gemm", act.data_ptr(), F2 // 2, w_down.data_ptr(), eo.data_ptr(), W, W, F2 // 2, meta.data_ptr(),
-                    E, max_tiles, is32, st)
+        gu = torch.empty(max_tiles * rows, F2, dtype=act_dtype, device=x.device)
+        eo = torch.empty(max_tiles * rows, W, dtype=act_dtype, device=x.device)
+        if tc5:
+            tile_expert, num_tiles = meta[2 * E + 2:], meta[2 * E:]
+            native.call("llmctl_gemm_bf16_grouped", xs.data_ptr(), w_gate_up.data_ptr(), gu.data_ptr(), max_tiles, F2, W, W, F2,
+                        tile_expert.data_ptr(), num_tiles.data_ptr(), E, st)
+            act = gated_silu(gu)
+            native.call("llmctl_gemm_bf16_grouped", act.data_ptr(), w_down.data_ptr(), eo.data_ptr(), max_tiles, W, F_, F_, W,
+                        tile_expert.data_ptr(), num_tiles.data_ptr(), E, st)
+        else:
+            native.call("llmctl_grouped_gemm", xs.data_ptr(), W, w_gate_up.data_ptr(), gu.data_ptr(), F2, F2, W, meta.data_ptr(), E,
+                        max_tiles, is32, st)
+            act = gated_silu(gu)
+            native.call("llmctl_grouped_gemm", act.data_ptr(), F_, w_down.data_ptr(), eo.data_ptr(), W, W, F_, meta.data_ptr(),
+                        E, max_tiles, is32, st)
         y = torch.empty(T, W, dtype=torch.float32, device=x.device)
         native.call("llmctl_moe_combine", eo.data_ptr(), W, pair_row.data_ptr(), wts.data_ptr(), top, int(not scale_input),
                     native.ptr(shared_out), native.ptr(gate), y.data_ptr(), T, is32, st)
