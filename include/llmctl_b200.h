@@ -210,6 +210,47 @@ int llmctl_comm_watchdog_poll(unsigned long long* out, char* module_name, int na
 int llmctl_comm_watchdog_set_timeout_ms(unsigned long long ms);
 int llmctl_comm_watchdog_modules(void);
 
+/* ---- Ragged-batch inference models (latent attention, post-norm residual, mixture of experts).  bf16 or fp32
+ * activations (is_fp32 / *_fp32 flags); norms, scores, routing, sums and the residual stream are fp32.
+ * Reference: none (the reference has no model code). ---- */
+/* x += gain * rmsnorm(y) on the fp32 stream; x_act receives the stream rounded to the activation type. */
+int llmctl_postnorm_residual(const void* y, int y_fp32, long long ldy, float* x, void* x_act, int act_fp32,
+                             const float* gain, int rows, int cols, float eps, void* stream);
+int llmctl_scalar_rmsnorm(const float* x, const long long* rows, void* out, int out_fp32, const float* gain, int n_out,
+                          int cols, float eps, void* stream);
+int llmctl_embed_scale(const long long* tokens, const void* table, int is_fp32, float scale, float* x, void* x_act,
+                       int rows, int cols, void* stream);
+int llmctl_softcap(float* v, long long n, float cap, void* stream);
+int llmctl_xielu(const void* z, void* out, int is_fp32, long long n, float a_pos, float a_neg, void* stream);
+int llmctl_gated_silu(const void* gate_up, long long ld, void* out, int is_fp32, int rows, int F, void* stream);
+/* d: [tokens, Q + R + dr] packed down-projections.  cq = rmsnorm(d[:, :Q]) * wq; the cache row of every token (slots)
+ * receives [rmsnorm(d[:, Q:Q+R]) * wkv | interleaved-pair rotation of d[:, Q+R:] at its position]. */
+int llmctl_latent_kv_write(const void* d, long long ld, int Q, int R, int dr, const void* wq, const void* wkv, void* cq,
+                           void* cache, const long long* slots, const int* positions, const float* freq, float mult,
+                           float eps, int tokens, int is_fp32, void* stream);
+int llmctl_latent_attention_uses_tensor_cores(int is_fp32, int R, int dr, int rows_per_tile);
+/* Attention of absorbed queries over the paged latent cache (see csrc/attention/latent_attention.cu). */
+int llmctl_latent_attention(const void* ql, int ql_bf16, long long ql_st, long long ql_sh, const void* q, long long ldq,
+                            int dn, const void* cache, const int* block_tables, int max_blocks, int block_size,
+                            const int* tiles, int ntiles, int tokens, const int* positions, const float* freq, float mult,
+                            float scale, int H, int R, int dr, int heads_per_tile, int splits, int keys_per_split,
+                            void* out, float* partial, int is_fp32, int tensor_cores, int rows_per_tile, void* stream);
+int llmctl_moe_tile_rows(void);
+int llmctl_moe_route(const float* x, const void* wr, const void* wg, int is_fp32, int tokens, int W, int E, int top,
+                     int softmax_scores, int renormalise, int* ids, float* weights, float* gate, int* counts, void* stream);
+/* meta: int32 [2 E + 2 + max_tiles] = { segment offsets[E] | cursors[E] | tiles | padded rows | tile -> expert }. */
+int llmctl_moe_plan(const int* counts, int E, int* meta, int max_tiles, int tile_rows, void* stream);
+int llmctl_moe_permute(const float* x, int W, const int* ids, const float* weights, int scale_input, int* meta, int E,
+                       int* pair_row, void* xs, int is_fp32, int tokens, int top, void* stream);
+int llmctl_grouped_gemm(const void* A, long long lda, const void* Wt, void* out, long long ldo, int N, int K,
+                        const int* meta, int E, int max_tiles, int is_fp32, void* stream);
+/* The tcgen05 GEMM over 128-row blocks of A, block i against expert tile_expert[i]'s [N, K] matrix. */
+int llmctl_gemm_bf16_grouped(const void* A, const void* W, void* C, int max_tiles, int N, int K, long long lda,
+                             long long ldc, const int* tile_expert, const int* num_tiles, int experts, void* stream);
+int llmctl_moe_combine(const void* expert_out, int W, const int* pair_row, const float* weights, int top,
+                       int scale_output, const void* shared_out, const float* gate, float* y, int tokens, int is_fp32,
+                       void* stream);
+
 #ifdef __cplusplus
 }
 #endif
