@@ -269,7 +269,8 @@ static int launch_latent_attention(const float* ql, long long ql_st, long long q
 }
 
 // ---- bf16 tensor-core variant ------------------------------------------------------------------------------------
-// Same tiling of the queries (16 rows per CTA, 8 warps); keys in tiles of 64 copied from the cache rows as they are.  Warp w
+// Same tiling of the queries (16 rows per CTA, 8 warps); keys in tiles of 64 copied from the cache rows as they are
+// (cp.async, double-buffered where shared memory allows).  Warp w
 // computes the scores of keys 8w..8w+7 (S = Q K^T over all R + dr columns), the softmax runs on S in shared memory,
 // P goes back as bf16 and warp w accumulates the columns [w * 8 NT, (w + 1) * 8 NT) of O += P C, where C is the first
 // R columns of the very same key tile (ldmatrix with transposition).
@@ -285,13 +286,13 @@ latent_attention_tc_kernel(const TQ* __restrict__ ql, long long ql_st, long long
                            const __nv_bfloat16* __restrict__ cache, const int* __restrict__ block_tables, int max_blocks,
                            int block_size, const int* __restrict__ tiles, const int* __restrict__ positions,
                            const float* __restrict__ freq, float mult, float scale, int H, int R, int dr, int heads_per_tile,
-                           int keys_per_split, __nv_bfloat16* __restrict__ out, float* __restrict__ partial) {
+                           int keys_per_split, int stages, __nv_bfloat16* __restrict__ out, float* __restrict__ partial) {
   constexpr int kR = 16 * MT, kWarps = 8 * MT;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int D = R + dr, Dp = D + 8;
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [kR][Dp]
-  __nv_bfloat16* Ks = Qs + kR * Dp;                                     // [kTcKeys][Dp]
-  float* Ss = reinterpret_cast<float*>(Ks + kTcKeys * Dp);              // [kR][kSsLd]
+  __nv_bfloat16* Ks0 = Qs + kR * Dp;                                    // [stages][kTcKeys][Dp]
+  float* Ss = reinterpret_cast<float*>(Ks0 + stages * kTcKeys * Dp);    // [kR][kSsLd]
   __nv_bfloat16* Ps = reinterpret_cast<__nv_bfloat16*>(Ss + kR * kSsLd);      // [kR][kPsLd]
   float* row_m = reinterpret_cast<float*>(Ps + kR * kPsLd);
   float* row_l = row_m + kR;
@@ -339,11 +340,11 @@ latent_attention_tc_kernel(const TQ* __restrict__ ql, long long ql_st, long long
   const int k_begin = split * keys_per_split;
   const int k_end = min(last + 1, k_begin + keys_per_split);
   const int vec_per_row = D >> 3;
-  for (int j0 = k_begin; j0 < k_end; j0 += kTcKeys) {
-    __syncthreads();
-    for (int jj = warp; jj < kTcKeys; jj += kWarps) {   // a warp per key row, asynchronous 16-byte copies
+  // a warp per key row, asynchronous 16-byte copies of the cache rows as they are
+  auto load_tile = [&](int j0, __nv_bfloat16* Kd) {
+    for (int jj = warp; jj < kTcKeys; jj += kWarps) {
       const int j = j0 + jj;
-      __nv_bfloat16* dst = Ks + jj * Dp;
+      __nv_bfloat16* dst = Kd + jj * Dp;
       if (j < k_end) {
         const long long slot = static_cast<long long>(bt[j / block_size]) * block_size + (j % block_size);
         const __nv_bfloat16* src = cache + slot * D;
@@ -353,7 +354,25 @@ latent_attention_tc_kernel(const TQ* __restrict__ ql, long long ql_st, long long
       }
     }
     cp_async_commit();
-    cp_async_wait_all();
+  };
+  // With two stages the copy of tile i + 1 is in flight while tile i is multiplied.
+  int buf = 0;
+  if (stages == 2 && k_begin < k_end) load_tile(k_begin, Ks0);
+  for (int j0 = k_begin; j0 < k_end; j0 += kTcKeys) {
+    __nv_bfloat16* Ks = Ks0 + buf * kTcKeys * Dp;
+    __syncthreads();                       // the previous tile's products are done: its buffer may be overwritten
+    if (stages == 2) {
+      if (j0 + kTcKeys < k_end) {
+        load_tile(j0 + kTcKeys, Ks0 + (buf ^ 1) * kTcKeys * Dp);
+        cp_async_wait_prior();
+      } else {
+        cp_async_wait_all();
+      }
+      buf ^= 1;
+    } else {
+      load_tile(j0, Ks);
+      cp_async_wait_all();
+    }
     __syncthreads();
     {
       float sacc[2][4] = {};                   // two independent accumulation chains over alternate k-steps
@@ -453,8 +472,8 @@ latent_attention_tc_kernel(const TQ* __restrict__ ql, long long ql_st, long long
   }
 }
 
-static size_t latent_attention_tc_smem(int R, int dr, int rows) {
-  return static_cast<size_t>(rows + kTcKeys) * (R + dr + 8) * 2 + static_cast<size_t>(rows) * (kSsLd * 4 + kPsLd * 2 + 16);
+static size_t latent_attention_tc_smem(int R, int dr, int rows, int stages = 1) {
+  return static_cast<size_t>(rows + stages * kTcKeys) * (R + dr + 8) * 2 + static_cast<size_t>(rows) * (kSsLd * 4 + kPsLd * 2 + 16);
 }
 
 static bool latent_attention_tc_ok(int R, int dr, int rows = kRows) {
@@ -468,7 +487,12 @@ static int launch_latent_attention_tc(const TQ* ql, long long ql_st, long long q
                                       const int* positions, const float* freq, float mult, float scale, int H, int R, int dr,
                                       int heads_per_tile, int splits, int keys_per_split, void* out, float* partial,
                                       int tokens, int rows, cudaStream_t s) {
-  const size_t smem = latent_attention_tc_smem(R, dr, rows);
+  // A second key-tile stage overlaps the copy of the next tile with the products of this one.  16-row tiles take it
+  // only while two CTAs still share an SM (they overlap each other's copies anyway); 32-row tiles whenever it fits
+  // (up to R + dr = 576 it does).
+  const size_t smem2 = latent_attention_tc_smem(R, dr, rows, 2);
+  const int stages = (rows == 32 ? smem2 <= 227 * 1024 : smem2 <= 113 * 1024) ? 2 : 1;
+  const size_t smem = latent_attention_tc_smem(R, dr, rows, stages);
   const int nt = (R + 63) / 64;
   dim3 grid(ntiles, (H + heads_per_tile - 1) / heads_per_tile, splits);
 #define LAUNCH_TC(NT, MT)                                                                                            \
@@ -478,7 +502,7 @@ static int launch_latent_attention_tc(const TQ* ql, long long ql_st, long long q
     if (e != cudaSuccess) return static_cast<int>(e);                                                                \
     kern<<<grid, 256 * MT, smem, s>>>(ql, ql_st, ql_sh, (const __nv_bfloat16*)q, ldq, dn, (const __nv_bfloat16*)cache, \
                                       block_tables, max_blocks, block_size, tiles, positions, freq, mult, scale,     \
-                                      H, R, dr, heads_per_tile, keys_per_split, (__nv_bfloat16*)out, partial);       \
+                                      H, R, dr, heads_per_tile, keys_per_split, stages, (__nv_bfloat16*)out, partial); \
   } while (0)
 #define LAUNCH_TC_NT(MT)          \
   do {                            \
