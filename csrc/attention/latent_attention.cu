@@ -237,6 +237,12 @@ latent_attention_merge_kernel(const float* __restrict__ partial, T* __restrict__
   }
 }
 
+// Used by the tcgen05 kernel's launcher (latent_attention_t5.cu) for split contexts.
+int launch_latent_attention_merge_bf16(const float* partial, void* out, int R, int splits, int rows, cudaStream_t s) {
+  latent_attention_merge_kernel<__nv_bfloat16><<<rows, 128, 0, s>>>(partial, (__nv_bfloat16*)out, R, splits);
+  return 0;
+}
+
 template <typename T>
 static int launch_latent_attention(const float* ql, long long ql_st, long long ql_sh, const void* q, long long ldq, int dn, const void* cache,
                                    const int* block_tables, int max_blocks, int block_size, const int* tiles, int ntiles,

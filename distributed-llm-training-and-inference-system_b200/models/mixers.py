@@ -95,7 +95,10 @@ class LatentAttention(nn.Module):
         else:
             ql = torch.bmm(qn.float(), self.w_uk.float())
         ql = ql.transpose(0, 1)
-        rows = lops.rows_per_tile(q.dtype, s.kv_rank, s.rot_dim, q.is_cuda, s.heads if batch.decode_only else lops.ROWS_PER_TILE_WIDE)
+        if lops.uses_tcgen05(q.dtype, s.kv_rank, s.rot_dim, cache.shape[1], q.is_cuda):
+            rows = lops.ROWS_PER_TILE_TCGEN05
+        else:
+            rows = lops.rows_per_tile(q.dtype, s.kv_rank, s.rot_dim, q.is_cuda, s.heads if batch.decode_only else lops.ROWS_PER_TILE_WIDE)
         ol = lops.latent_attention(ql, q, s.dim, cache, batch.block_tables, batch.tiles(rows), batch.positions,
                                    self.rot_freq, self.rot_mult, s.scale, batch.heads_per_tile(s.heads, rows), batch.max_context,
                                    batch.attention_splits(s.heads, rows), rows=rows)

@@ -22,15 +22,36 @@ native.register_signature("llmctl_latent_attention", [c_void_p, c_int, c_ll, c_l
                                                        c_int, c_int, c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_int,
                                                        c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
 native._KERNELS_PER_CALL["llmctl_latent_attention"] = 1
+native.register_signature("llmctl_latent_attention_t5_ok", [c_int, c_int, c_int])
+native.register_signature("llmctl_latent_attention_t5_status", [c_int])
+native.register_signature("llmctl_latent_attention_t5", [c_void_p, c_int, c_ll, c_ll, c_void_p, c_ll, c_int, c_void_p, c_ll, c_void_p, c_int, c_int,
+                                                          c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_int,
+                                                          c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+native._KERNELS_PER_CALL["llmctl_latent_attention_t5"] = 2
 
 ROWS_PER_TILE = 16          # query rows (token, head) a CTA owns; tiles are built by the engine with this limit
 ROWS_PER_TILE_WIDE = 32     # the tensor-core kernel also takes tiles of 32 rows (half the key traffic per row)
+ROWS_PER_TILE_TCGEN05 = 128     # query rows per CTA of the tcgen05 kernel (UMMA M)
+TILE_WIDTHS = (ROWS_PER_TILE, ROWS_PER_TILE_WIDE, ROWS_PER_TILE_TCGEN05)
 
 
 def uses_tensor_cores(dtype: torch.dtype, R: int, dr: int) -> bool:
     """bf16 with these sizes runs the mma.sync kernel (which also takes bf16 absorbed queries); same rule as
     llmctl_latent_attention_uses_tensor_cores."""
     return dtype == torch.bfloat16 and (R + dr) % 16 == 0 and R % 8 == 0 and R <= 512
+
+
+def uses_tcgen05(dtype: torch.dtype, R: int, dr: int, block_size: int, cuda: bool) -> bool:
+    """bf16 on a GPU with latent and rope widths that are whole 128-byte swizzle panels (R and R + dr multiples of 64,
+    R + dr <= 576) and pages of whole 32-key tiles: the tcgen05 kernel (csrc/attention/latent_attention_t5.cu)."""
+    if not (cuda and dtype == torch.bfloat16 and native.has_symbol("llmctl_latent_attention_t5")):
+        return False
+    return bool(native.lib().llmctl_latent_attention_t5_ok(int(R), int(dr), int(block_size)))
+
+
+def tcgen05_status(clear: bool = True) -> int:
+    """0 unless a bounded wait of the tcgen05 kernel ran out since the last clearing call (synchronises the device)."""
+    return int(native.lib().llmctl_latent_attention_t5_status(int(clear)))
 
 
 def rows_per_tile(dtype: torch.dtype, R: int, dr: int, cuda: bool, rows_wanted: int = ROWS_PER_TILE_WIDE) -> int:
@@ -83,12 +104,20 @@ def latent_attention(ql: torch.Tensor, q: torch.Tensor, dn: int, cache: torch.Te
     block_size = cache.shape[1]
     if q.is_cuda:
         assert ql.stride(2) == 1 and q.stride(1) == 1 and cache.is_contiguous()
-        assert ql.dtype == torch.float32 or (tensor_cores and uses_tensor_cores(q.dtype, R, dr))
+        assert ql.dtype == torch.float32 or (tensor_cores and (uses_tensor_cores(q.dtype, R, dr) or rows == ROWS_PER_TILE_TCGEN05))
         out = torch.empty(T, H, R, dtype=q.dtype, device=q.device)
         splits = max(1, int(splits))
         per = (max_context + splits - 1) // splits
         per = max(64, (per + 63) // 64 * 64)
         partial = torch.empty(T * H * splits * (R + 2), dtype=torch.float32, device=q.device) if splits > 1 else None
+        if rows == ROWS_PER_TILE_TCGEN05:
+            qfull = torch.empty(T, H, D, dtype=torch.bfloat16, device=q.device)
+            native.call("llmctl_latent_attention_t5", ql.data_ptr(), int(ql.dtype == torch.bfloat16), ql.stride(0), ql.stride(1),
+                        q.data_ptr(), q.stride(0), dn, cache.data_ptr(), cache.shape[0] * block_size, block_tables.data_ptr(),
+                        block_tables.shape[1], block_size, tiles.data_ptr(), tiles.shape[0], T, positions.data_ptr(),
+                        freq.data_ptr(), float(mult), float(scale), H, R, dr, heads_per_tile, splits, per, qfull.data_ptr(),
+                        out.data_ptr(), native.ptr(partial), native.stream_ptr())
+            return out
         native.call("llmctl_latent_attention", ql.data_ptr(), int(ql.dtype == torch.bfloat16), ql.stride(0), ql.stride(1),
                     q.data_ptr(), q.stride(0), dn, cache.data_ptr(),
                     block_tables.data_ptr(), block_tables.shape[1], block_size, tiles.data_ptr(), tiles.shape[0], T,

@@ -100,7 +100,7 @@ def _kernels(size: Dict[str, Any], peaks: Dict[str, float]) -> Dict[str, Any]:
         T = b.num_tokens
         ql = torch.randn(T, H, R, device=dev)
         q = torch.randn(T, H * (dn + dr), device=dev).to(torch.bfloat16)
-        rows = L.rows_per_tile(q.dtype, R, dr, True, H if new == 1 else 32)                     # the tiling and query type the model path takes
+        rows = L.ROWS_PER_TILE_TCGEN05 if L.uses_tcgen05(q.dtype, R, dr, bs, True) else L.rows_per_tile(q.dtype, R, dr, True, H if new == 1 else 32)                     # the tiling and query type the model path takes
         if L.uses_tensor_cores(q.dtype, R, dr):
             ql = ql.to(torch.bfloat16)
         t = _time(lambda: L.latent_attention(ql, q, dn, cache, b.block_tables, b.tiles(rows), b.positions, freq, mult, 0.07,

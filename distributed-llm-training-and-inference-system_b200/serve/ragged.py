@@ -13,7 +13,7 @@ from typing import List, Optional, Sequence as Seq, Tuple
 import numpy as np
 import torch
 
-from ..ops.latent_attention import ROWS_PER_TILE, ROWS_PER_TILE_WIDE
+from ..ops.latent_attention import ROWS_PER_TILE, TILE_WIDTHS
 
 
 @dataclass
@@ -37,12 +37,13 @@ class RaggedBatch:
                  pad_to: Optional[Tuple[int, int, int]] = None):
         self.block_size, self.device, self._sms, self.pad_to = block_size, device, sm_count, pad_to
         self.decode_only = all(len(p.tokens) == 1 for p in portions)
-        # attention query tiles come in two widths: 16 rows, and 32 rows for kernels that take them
-        self._tile_tokens = (1, 1) if self.decode_only else (ROWS_PER_TILE, ROWS_PER_TILE_WIDE)
+        # attention query tiles come in the widths the kernels take (16 / 32 / 128 rows); a tile of a decode-only batch
+        # is one token with as many of its heads as fit
+        self._tile_tokens = tuple(1 if self.decode_only else w for w in TILE_WIDTHS)
         if pad_to is not None:
             assert self.decode_only and len(portions) <= pad_to[0]
             T = B = n_out = pad_to[0]
-            ntiles = (T, T)
+            ntiles = (T,) * len(TILE_WIDTHS)
             max_blocks, self.max_context = pad_to[1], pad_to[2]
         else:
             T = sum(len(p.tokens) for p in portions)
@@ -52,14 +53,14 @@ class RaggedBatch:
             max_blocks = max(len(p.block_table) for p in portions)
             n_out = sum(len(p.want) for p in portions)
             ntiles = tuple(sum((len(p.tokens) + w - 1) // w for p in portions) for w in self._tile_tokens)
-        # int32 words: tokens(2T) | slots(2T) | out_rows(2 n_out) | positions(T) | tiles(4 n16) | block tables(B max_blocks) | wide tiles(4 n32)
-        sizes = [2 * T, 2 * T, 2 * n_out, T, 4 * ntiles[0], B * max_blocks, 4 * ntiles[1]]
+        # int32 words: tokens(2T) | slots(2T) | out_rows(2 n_out) | positions(T) | block tables(B max_blocks) | tiles(4 n) per width
+        sizes = [2 * T, 2 * T, 2 * n_out, T, B * max_blocks] + [4 * n for n in ntiles]
         offs = np.concatenate([[0], np.cumsum(sizes)])
         self._host = torch.zeros(int(offs[-1]), dtype=torch.int32, pin_memory=device.type == "cuda")
         a = self._host.numpy()
         self._h = (a[offs[0]:offs[1]].view(np.int64), a[offs[1]:offs[2]].view(np.int64), a[offs[2]:offs[3]].view(np.int64),
-                   a[offs[3]:offs[4]], (a[offs[4]:offs[5]].reshape(ntiles[0], 4), a[offs[6]:offs[7]].reshape(ntiles[1], 4)),
-                   a[offs[5]:offs[6]].reshape(B, max_blocks))
+                   a[offs[3]:offs[4]], tuple(a[offs[5 + k]:offs[6 + k]].reshape(n, 4) for k, n in enumerate(ntiles)),
+                   a[offs[4]:offs[5]].reshape(B, max_blocks))
         dev = torch.empty_like(self._host, device=device) if device.type == "cuda" else self._host
         self._dev = dev
         self.nbytes = self._host.numel() * 4
@@ -68,8 +69,8 @@ class RaggedBatch:
         self.slots = dev[offs[1]:offs[2]].view(torch.int64)
         self.out_rows = dev[offs[2]:offs[3]].view(torch.int64)
         self.positions = dev[offs[3]:offs[4]]
-        self._tiles = {ROWS_PER_TILE: dev[offs[4]:offs[5]].view(ntiles[0], 4), ROWS_PER_TILE_WIDE: dev[offs[6]:offs[7]].view(ntiles[1], 4)}
-        self.block_tables = dev[offs[5]:offs[6]].view(B, max_blocks)
+        self._tiles = {w: dev[offs[5 + k]:offs[6 + k]].view(ntiles[k], 4) for k, w in enumerate(TILE_WIDTHS)}
+        self.block_tables = dev[offs[4]:offs[5]].view(B, max_blocks)
         self.refill(portions)
 
     def refill(self, portions: List[Portion]) -> None:
@@ -83,10 +84,11 @@ class RaggedBatch:
             positions[:] = 0
             tables[:] = 0
             for r in range(self.pad_to[0]):                 # padding rows too: one tile and one (ignored) logits row each
-                tiles[0][r] = tiles[1][r] = (r, 1, r, 0)
+                for tl in tiles:
+                    tl[r] = (r, 1, r, 0)
                 out_rows[r] = r
         t = o = 0
-        ti = [0, 0]
+        ti = [0] * len(tiles)
         for b, p in enumerate(portions):
             n = len(p.tokens)
             bt = np.asarray(p.block_table, dtype=np.int64)

@@ -105,6 +105,50 @@ def test_latent_attention_kernels(cuda_device, dt, H, dn, dr, R, Q, bs):
     close(cache_g, cache, dt, 4)
 
 
+@pytest.mark.parametrize("H,dn,dr,R,bs", [(16, 8, 64, 512, 64), (3, 16, 64, 64, 32), (40, 8, 64, 128, 64), (1, 4, 128, 320, 96)])
+def test_latent_attention_tcgen05(cuda_device, H, dn, dr, R, bs):
+    """The tcgen05 kernel against the PyTorch restatement: whole prompts of unequal length in one batch (128-token
+    tiles that end inside pages and inside 32-key tiles), portions that continue them, and decode-only batches with
+    one and with several key splits; scores spread widely so that the running reference is rescaled."""
+    from llmctl_b200.ops import latent_attention as L
+    from llmctl_b200.ops.elementwise import rope_frequencies
+    from llmctl_b200.serve.ragged import Portion, RaggedBatch
+    dt = torch.bfloat16
+    assert L.uses_tcgen05(dt, R, dr, bs, True)
+    g = torch.Generator().manual_seed(7)
+    freq, mult = rope_frequencies(dr, 10000.0, None)
+    lens = [300, 64, 1, 129, 33]
+    nb = sum((n + bs - 1) // bs for n in lens) + 3
+    perm = torch.randperm(nb, generator=g).tolist()
+    tables, used = [], 0
+    for n in lens:
+        k = (n + bs - 1) // bs
+        tables.append(perm[used:used + k])
+        used += k
+    cache = (torch.randn(nb, bs, R + dr, generator=g) * 0.5).to(dt)
+    cache_g = cache.cuda()
+    rows = L.ROWS_PER_TILE_TCGEN05
+    batches = {
+        "whole": [Portion(i, [0] * n, 0, [], tables[i]) for i, n in enumerate(lens)],
+        "portions": [Portion(i, [0] * min(n, 37), n - min(n, 37), [], tables[i]) for i, n in enumerate(lens)],
+        "decode": [Portion(i, [0], n - 1, [], tables[i]) for i, n in enumerate(lens)],
+    }
+    for name, portions in batches.items():
+        for splits in ((1, 3) if name == "decode" else (1,)):
+            bc = RaggedBatch(portions, bs, torch.device("cpu"))
+            bg = RaggedBatch(portions, bs, torch.device("cuda"))
+            T = bc.num_tokens
+            ql = (torch.randn(T, H, R, generator=g) * 0.4).to(dt)
+            q = torch.randn(T, H * (dn + dr), generator=g).to(dt)
+            ref = L.latent_attention(ql.float(), q, dn, cache, bc.block_tables, bc.tiles(), bc.positions, freq, mult, 0.25,
+                                     bc.heads_per_tile(H), bc.max_context)
+            out = L.latent_attention(ql.cuda(), q.cuda(), dn, cache_g, bg.block_tables, bg.tiles(rows), bg.positions, freq.cuda(),
+                                     mult, 0.25, bg.heads_per_tile(H, rows), bg.max_context, splits, rows=rows)
+            torch.cuda.synchronize()
+            assert L.tcgen05_status() == 0, f"{name}: a bounded wait ran out"
+            close(out, ref, dt, 4)
+
+
 @pytest.mark.parametrize("dt", DTYPES)
 @pytest.mark.parametrize("T,E,top,scale_input", [(70, 5, 2, True), (3, 8, 1, True), (200, 3, 3, False), (700, 6, 2, True)])
 def test_moe_kernels(cuda_device, dt, T, E, top, scale_input):
