@@ -95,7 +95,9 @@ class LatentAttention(nn.Module):
         else:
             ql = torch.bmm(qn.float(), self.w_uk.float())
         ql = ql.transpose(0, 1)
-        if lops.uses_tcgen05(q.dtype, s.kv_rank, s.rot_dim, cache.shape[1], q.is_cuda):
+        # batches with prompt portions fill the tcgen05 kernel's 128-row tiles; a decoding token has only its heads to
+        # offer, and the 16 / 32-row kernel reads the cache once for them
+        if not batch.decode_only and lops.uses_tcgen05(q.dtype, s.kv_rank, s.rot_dim, cache.shape[1], q.is_cuda):
             rows = lops.ROWS_PER_TILE_TCGEN05
         else:
             rows = lops.rows_per_tile(q.dtype, s.kv_rank, s.rot_dim, q.is_cuda, s.heads if batch.decode_only else lops.ROWS_PER_TILE_WIDE)
