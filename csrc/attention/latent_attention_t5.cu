@@ -182,9 +182,8 @@ latent_attention_t5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
       const uint32_t idesc_pv = make_idesc_bf16(kRows, static_cast<uint32_t>(ncols), 0u, 1u);    // A from TMEM, B MN-major
       const uint32_t q_addr = smem_base;
       bool ok = wait_or_abort(&bar_q, 0, abort, 2);
-      auto issue_s = [&](int i) -> bool {
+      auto issue_s = [&](int i) {
         const int st = i & 1;
-        if (!wait_or_abort(&bar_kfull[st], (i >> 1) & 1, abort, 3)) return false;
         tc_fence_after();
         const uint32_t k_addr = smem_base + q_bytes + st * k_bytes;
         const uint32_t d = tmem_base + kSCol + st * kKeys;
@@ -194,12 +193,8 @@ latent_attention_t5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
                      make_smem_desc(k_addr + (ks >> 2) * kKPanel + inner, 16, 1024, 2), idesc_s, ks != 0 ? 1u : 0u);
         }
         umma_commit<1>(&bar_s[st]);
-        return true;
       };
-      ok = ok && issue_s(0);
-      for (int i = 0; ok && i < ntile; ++i) {
-        if (i + 1 < ntile && !issue_s(i + 1)) break;
-        if (!wait_or_abort(&bar_p, i & 1, abort, 4)) break;
+      auto issue_pv = [&](int i) {
         tc_fence_after();
         const int st = i & 1;
         const uint32_t v_addr = smem_base + q_bytes + st * k_bytes + (col0 >> 6) * kKPanel;
@@ -208,8 +203,33 @@ latent_attention_t5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
         for (int ks = 0; ks < kKeys / 16; ++ks)
           umma_ts<1>(tmem_base, tP + ks * 8, make_smem_desc(v_addr + ks * 2048, kKPanel, 1024, 2), idesc_pv,
                      (i | ks) != 0 ? 1u : 0u);
-        umma_commit<1>(&bar_kempty[st]);
-        umma_commit<1>(&bar_pv);
+        umma_commit<1>(&bar_kempty[st]);      // the stage is free for tile i + 2 ...
+        umma_commit<1>(&bar_pv);              // ... and O is complete up to tile i
+      };
+      // Whichever is ready goes first: the scores of the next tile (its keys have landed, and the value product that
+      // last read its S / P buffer has been issued) or the value product of the oldest tile whose P is in place.
+      // Issuing P V as soon as P is there frees the key stage early, so both stages' copies are in flight together.
+      int next_s = 0, next_pv = 0;
+      long long t0 = clock64();
+      uint32_t spins = 0;
+      while (ok && next_pv < ntile) {
+        if (next_s < ntile && next_s <= next_pv + 1 && mbar_try_wait(&bar_kfull[next_s & 1], (next_s >> 1) & 1)) {
+          issue_s(next_s++);
+        } else if (next_s > next_pv && mbar_try_wait(&bar_p, next_pv & 1)) {
+          issue_pv(next_pv++);
+        } else {
+          if ((++spins & 63u) == 0u) {
+            if (*abort) break;
+            if (clock64() - t0 > kWaitCycles) {
+              *abort = 1;
+              atomicCAS(&g_status, 0u, 0x100u | 3u);
+              break;
+            }
+          }
+          continue;
+        }
+        t0 = clock64();
+        spins = 0;
       }
     }
   } else {
