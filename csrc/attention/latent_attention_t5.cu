@@ -158,15 +158,20 @@ latent_attention_t5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
       const int qrow0 = q_rows_are_heads ? tok0 * H + h0 : tok0;
       for (int p = 0; p < panels; ++p) tma_load_2d(smem + p * kQPanel, &tmQ, &bar_q, qcol0 + 64 * p, qrow0);
       int issued = 0;
+      auto slot_of = [&](int i) {
+        const int j0 = k_begin + kKeys * i;
+        return bt[j0 / block_size] * block_size + j0 % block_size;
+      };
+      int slot = slot_of(0);
       for (int i = 0; i < ntile; ++i) {
         const int st = i & 1;
+        const int slot_next = i + 1 < ntile ? slot_of(i + 1) : 0;     // the page lookup overlaps the wait for the stage
         if (!wait_or_abort(&bar_kempty[st], ((i >> 1) & 1) ^ 1, abort, 1)) break;
         mbar_expect_tx(&bar_kfull[st], k_bytes);
-        const int j0 = k_begin + kKeys * i;
-        const int slot = bt[j0 / block_size] * block_size + j0 % block_size;
         uint8_t* ks = smem + q_bytes + st * k_bytes;
         for (int p = 0; p < panels; ++p) tma_load_2d(ks + p * kKPanel, &tmK, &bar_kfull[st], 64 * p, slot);
         ++issued;
+        slot = slot_next;
       }
       if (*abort) {      // let the copies in flight land before the CTA's shared memory is given back
         int none = 0;
@@ -182,15 +187,20 @@ latent_attention_t5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
       const uint32_t idesc_pv = make_idesc_bf16(kRows, static_cast<uint32_t>(ncols), 0u, 1u);    // A from TMEM, B MN-major
       const uint32_t q_addr = smem_base;
       bool ok = wait_or_abort(&bar_q, 0, abort, 2);
+      // Descriptors are linear in the start address (a 16-byte unit in their low bits), so the issue loop only adds:
+      // one thread issues all 36 score products of a tile, and every scalar instruction between two of them is on the
+      // critical path of the whole CTA.
+      const uint64_t q_desc0 = make_smem_desc(q_addr, 16, 1024, 2);
       auto issue_s = [&](int i) {
         const int st = i & 1;
         tc_fence_after();
-        const uint32_t k_addr = smem_base + q_bytes + st * k_bytes;
         const uint32_t d = tmem_base + kSCol + st * kKeys;
-        for (int ks = 0; ks < (D >> 4); ++ks) {
-          const uint32_t inner = (ks & 3) * 32;
-          umma_ss<1>(d, make_smem_desc(q_addr + (ks >> 2) * kQPanel + inner, 16, 1024, 2),
-                     make_smem_desc(k_addr + (ks >> 2) * kKPanel + inner, 16, 1024, 2), idesc_s, ks != 0 ? 1u : 0u);
+        uint64_t dq = q_desc0, dk = make_smem_desc(smem_base + q_bytes + st * k_bytes, 16, 1024, 2);
+        for (int p = 0; p < panels; ++p) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) umma_ss<1>(d, dq + 2 * j, dk + 2 * j, idesc_s, (p | j) != 0 ? 1u : 0u);
+          dq += kQPanel >> 4;
+          dk += kKPanel >> 4;
         }
         umma_commit<1>(&bar_s[st]);
       };
