@@ -50,18 +50,18 @@ def _serve(cfg, prompts: List[List[int]], new_tokens: int, block_size: int) -> D
     blocks = (total + block_size - 1) // block_size + 2 * len(prompts)
     eng = InferenceEngine(cfg, max_batch_size=len(prompts), max_batch_tokens=max(8192, total), device="cuda", kv_block_size=block_size,
                           num_kv_blocks=blocks)
-    rounds: List[Dict[str, float]] = []
-    for rnd in range(4):                   # the first round warms up (tensor maps, graphs, allocator); median of the other three
+    passes: List[Dict[str, float]] = []
+    for rnd in range(4):                   # the first pass warms up (tensor maps, graphs, allocator); median of the other three
         for k in ("prefill_tokens", "decode_tokens", "prefill_time_s", "decode_time_s", "decode_steps"):
             eng.stats[k] = 0 if "time" not in k else 0.0
         torch.cuda.synchronize()
         eng.generate(prompts, max_tokens=new_tokens if rnd else 4, temperature=0.0)
         torch.cuda.synchronize()
         s = eng.stats
-        rounds.append({"prefill_tok_s": s["prefill_tokens"] / max(s["prefill_time_s"], 1e-9),
+        passes.append({"prefill_tok_s": s["prefill_tokens"] / max(s["prefill_time_s"], 1e-9),
                        "decode_tok_s": s["decode_tokens"] / max(s["decode_time_s"], 1e-9),
                        "decode_ms_per_step": 1e3 * s["decode_time_s"] / max(s["decode_steps"], 1)})
-    out = {k: sorted(r[k] for r in rounds[1:])[1] for k in rounds[0]}
+    out = {k: sorted(r[k] for r in passes[1:])[1] for k in passes[0]}
     del eng
     torch.cuda.empty_cache()
     return out
