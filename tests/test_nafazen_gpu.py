@@ -180,24 +180,49 @@ def _engine(cfg, weights, dt, device, blocks=12, bs=16):
     return eng
 
 
+GPU_CONFIGS = {
+    "example": (dict(), 16),
+    # sizes that are no multiples of 8 (library matrix products, FMA attention and grouped-GEMM kernels), one head, top 1
+    "odd": (dict(width=40, heads=1, dim=6, rot_dim=2, vdim=10, kv_rank=48, q_rank=5, ff=20, experts=3, top=1, expert_ff=8,
+                 shared_ff=None, pattern="bMcDa-", softcap=None, embedding_scale=0.5), 16),
+    # latent and rope widths of whole 64-column panels on 64-token pages: prompt portions run on the tcgen05 kernel
+    "panels": (dict(width=128, heads=3, dim=16, rot_dim=64, vdim=24, kv_rank=64, q_rank=40, ff=96, experts=4, top=2, expert_ff=32,
+                    shared_ff=48, pattern="aDbMcM"), 64),
+    "many_heads": (dict(width=48, heads=20, dim=4, rot_dim=6, vdim=3, kv_rank=10, q_rank=16, experts=6, top=3, pattern="aMbDcMcD",
+                        yarn=False), 32),
+}
+
+
+@pytest.mark.parametrize("name", sorted(GPU_CONFIGS))
 @pytest.mark.parametrize("dt", DTYPES)
-def test_model_matches_oracle_on_gpu(cuda_device, dt):
+def test_model_matches_oracle_on_gpu(cuda_device, dt, name):
     """Whole prompt, then portions + token-by-token decoding of the same prompt through the paged cache, and a mixed
     batch of two requests, all against the oracle's logits."""
     from llmctl_b200.models.nafazen import example_config
-    cfg = example_config()
+    kw, bs = GPU_CONFIGS[name]
+    cfg = example_config(**kw)
     w = oracle.random_weights(cfg, seed=3)
     torch.manual_seed(5)
     toks = torch.randint(0, cfg["vocab"], (75,)).tolist()
     ref = oracle.forward(cfg, w, toks, exact=True)
+    flips = []
+
     def same(a, b):
         if dt == torch.float32:
             return (a - b).abs().max().item() < 3e-4
-        return float((a - b).pow(2).mean().sqrt() / b.pow(2).mean().sqrt()) < 0.15       # bf16, tiny widths: rounding is a few % of the rms
-    eng = _engine(copy.deepcopy(cfg), w, dt, "cuda")
+        # bf16, tiny widths: rounding is a few % of a row's rms.  A router score that is a near tie in fp32 may pick
+        # another expert after rounding and move one token's logits as a whole: at most two such rows per scenario.
+        err = (a - b).pow(2).mean(-1).sqrt() / b.pow(2).mean(-1).sqrt()
+        flips.extend(err[err >= 0.15].tolist())
+        return len(flips) <= 2 and float(err[err < 0.15].mean() if (err < 0.15).any() else 0.0) < 0.05
+    eng = _engine(copy.deepcopy(cfg), w, dt, "cuda", blocks=max(4, 192 // bs), bs=bs)
     assert eng.kv.allocate(1, len(toks))
     got = eng.forward_portions([eng.portion(1, toks, 0, list(range(len(toks))))]).cpu()
     assert same(got, ref)
+    if name == "panels" and dt == torch.bfloat16:
+        from llmctl_b200.ops import latent_attention as L
+        m = cfg["layers"][0]["mixer"]
+        assert L.uses_tcgen05(dt, m["kv_rank"], m["rot_dim"], bs, True) and L.tcgen05_status() == 0
     eng.kv.free(1)
     # portions of 16 + 2 + 30, then decode; a second request rides along in the same batches
     other = toks[10:40]
