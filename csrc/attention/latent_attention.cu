@@ -219,27 +219,35 @@ __global__ void __launch_bounds__(128)
 latent_attention_merge_kernel(const float* __restrict__ partial, T* __restrict__ out, int R, int nsplit) {
   const long long base = blockIdx.x;   // token * H + head
   const float* p = partial + base * nsplit * (R + 2);
-  float gm = -INFINITY;
-  for (int s = 0; s < nsplit; ++s) gm = fmaxf(gm, p[s * (R + 2) + R]);
-  float gl = 0.f;
-  for (int s = 0; s < nsplit; ++s) {
-    const float ms = p[s * (R + 2) + R];
-    if (ms != -INFINITY) gl += p[s * (R + 2) + R + 1] * expf(ms - gm);
+  extern __shared__ float wsplit[];    // [nsplit]: exp(m_s - max m) / sum, 0 for empty splits
+  __shared__ float s_inv;
+  if (threadIdx.x < 32) {              // one warp: the maximum and the normaliser, in a fixed order
+    float gm = -INFINITY;
+    for (int s = threadIdx.x; s < nsplit; s += 32) gm = fmaxf(gm, p[s * (R + 2) + R]);
+    gm = warp_max(gm);
+    for (int s = threadIdx.x; s < nsplit; s += 32) {
+      const float ms = p[s * (R + 2) + R];
+      wsplit[s] = ms != -INFINITY ? expf(ms - gm) : 0.f;
+    }
+    __syncwarp();
+    if (threadIdx.x == 0) {
+      float gl = 0.f;
+      for (int s = 0; s < nsplit; ++s) gl += p[s * (R + 2) + R + 1] * wsplit[s];
+      s_inv = gl > 0.f ? 1.f / gl : 0.f;
+    }
   }
-  const float inv = gl > 0.f ? 1.f / gl : 0.f;
+  __syncthreads();
+  const float inv = s_inv;
   for (int c = threadIdx.x; c < R; c += blockDim.x) {
     float a = 0.f;
-    for (int s = 0; s < nsplit; ++s) {
-      const float ms = p[s * (R + 2) + R];
-      if (ms != -INFINITY) a += p[s * (R + 2) + c] * expf(ms - gm);
-    }
+    for (int s = 0; s < nsplit; ++s) a += p[s * (R + 2) + c] * wsplit[s];
     out[base * R + c] = from_f32<T>(a * inv);
   }
 }
 
 // Used by the tcgen05 kernel's launcher (latent_attention_t5.cu) for split contexts.
 int launch_latent_attention_merge_bf16(const float* partial, void* out, int R, int splits, int rows, cudaStream_t s) {
-  latent_attention_merge_kernel<__nv_bfloat16><<<rows, 128, 0, s>>>(partial, (__nv_bfloat16*)out, R, splits);
+  latent_attention_merge_kernel<__nv_bfloat16><<<rows, 128, splits * sizeof(float), s>>>(partial, (__nv_bfloat16*)out, R, splits);
   return 0;
 }
 
@@ -270,7 +278,7 @@ static int launch_latent_attention(const float* ql, long long ql_st, long long q
   else return static_cast<int>(cudaErrorInvalidValue);
 #undef LAUNCH
   if (splits > 1)
-    latent_attention_merge_kernel<T><<<tokens * H, 128, 0, s>>>(partial, (T*)out, R, splits);
+    latent_attention_merge_kernel<T><<<tokens * H, 128, splits * sizeof(float), s>>>(partial, (T*)out, R, splits);
   return 0;
 }
 
@@ -522,7 +530,7 @@ static int launch_latent_attention_tc(const TQ* ql, long long ql_st, long long q
 #undef LAUNCH_TC_NT
 #undef LAUNCH_TC
   if (splits > 1)
-    latent_attention_merge_kernel<__nv_bfloat16><<<tokens * H, 128, 0, s>>>(partial, (__nv_bfloat16*)out, R, splits);
+    latent_attention_merge_kernel<__nv_bfloat16><<<tokens * H, 128, splits * sizeof(float), s>>>(partial, (__nv_bfloat16*)out, R, splits);
   return 0;
 }
 

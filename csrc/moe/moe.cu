@@ -28,7 +28,7 @@ constexpr int kTileM = 64, kTileN = 64, kTileK = 16;
 
 // x: fp32 [tokens, W] (the residual stream); wr: [E, W]; wg: [W] or null.
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 moe_route_kernel(const float* __restrict__ x, const T* __restrict__ wr, const T* __restrict__ wg, int W, int E, int top,
                  int softmax_scores, int renormalise, int* __restrict__ ids, float* __restrict__ weights,
                  float* __restrict__ gate, int* __restrict__ counts) {
@@ -38,8 +38,18 @@ moe_route_kernel(const float* __restrict__ x, const T* __restrict__ wr, const T*
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
   for (int e = warp; e < E + (wg ? 1 : 0); e += nwarp) {
     const T* w = e < E ? wr + static_cast<long long>(e) * W : wg;
-    float s = 0.f;
-    for (int c = lane; c < W; c += 32) s += xr[c] * to_f32(w[c]);
+    // four independent partial sums per lane: the loads of a row are in flight together (a decode step routes a
+    // handful of tokens, so the kernel is pure latency); the order of the sum is fixed by W alone
+    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    int c = lane;
+    for (; c + 96 < W; c += 128) {
+      s0 += xr[c] * to_f32(w[c]);
+      s1 += xr[c + 32] * to_f32(w[c + 32]);
+      s2 += xr[c + 64] * to_f32(w[c + 64]);
+      s3 += xr[c + 96] * to_f32(w[c + 96]);
+    }
+    for (; c < W; c += 32) s0 += xr[c] * to_f32(w[c]);
+    float s = (s0 + s1) + (s2 + s3);
     s = warp_sum(s);
     if (lane == 0) {
       if (e < E) score[e] = s;
@@ -259,7 +269,7 @@ LLMCTL_API int llmctl_moe_route(const float* x, const void* wr, const void* wg, 
   cudaStream_t s = (cudaStream_t)stream;
   LLMCTL_CHECK(cudaMemsetAsync(counts, 0, sizeof(int) * E, s));
   if (tokens == 0) return 0;
-  LLMCTL_DISPATCH_DTYPE(is_fp32, T, (moe_route_kernel<T><<<tokens, 128, E * sizeof(float), s>>>(
+  LLMCTL_DISPATCH_DTYPE(is_fp32, T, (moe_route_kernel<T><<<tokens, 256, E * sizeof(float), s>>>(
                                         x, (const T*)wr, (const T*)wg, W, E, top, softmax_scores, renormalise, ids, weights, gate, counts)));
   LLMCTL_RETURN_LAST();
 }
