@@ -235,6 +235,15 @@ int llmctl_latent_attention(const void* ql, int ql_bf16, long long ql_st, long l
                             const int* tiles, int ntiles, int tokens, const int* positions, const float* freq, float mult,
                             float scale, int H, int R, int dr, int heads_per_tile, int splits, int keys_per_split,
                             void* out, float* partial, int is_fp32, int tensor_cores, int rows_per_tile, void* stream);
+/* The tcgen05 kernel (128-row query tiles): sizes that qualify, status of its bounded waits, and the launch.
+ * qfull: bf16 scratch [tokens, H, R + dr]; cache_rows = blocks x block_size. */
+int llmctl_latent_attention_t5_ok(int R, int dr, int block_size);
+int llmctl_latent_attention_t5_status(int clear);
+int llmctl_latent_attention_t5(const void* ql, int ql_bf16, long long ql_st, long long ql_sh, const void* q, long long ldq,
+                               int dn, const void* cache, long long cache_rows, const int* block_tables, int max_blocks,
+                               int block_size, const int* tiles, int ntiles, int tokens, const int* positions,
+                               const float* freq, float mult, float scale, int H, int R, int dr, int heads_per_tile,
+                               int splits, int keys_per_split, void* qfull, void* out, float* partial, void* stream);
 int llmctl_moe_tile_rows(void);
 int llmctl_moe_route(const float* x, const void* wr, const void* wg, int is_fp32, int tokens, int W, int E, int top,
                      int softmax_scores, int renormalise, int* ids, float* weights, float* gate, int* counts, void* stream);
