@@ -149,6 +149,52 @@ def test_latent_attention_tcgen05(cuda_device, H, dn, dr, R, bs):
             close(out, ref, dt, 4)
 
 
+@pytest.mark.parametrize("kind", ["fp32", "bf16_rows16", "bf16_rows32", "bf16_tcgen05"])
+def test_far_key_decides_on_every_kernel(cuda_device, kind):
+    """One key far back carries a score that stands out (its query and key coordinates are scaled up) and a value unlike
+    all others: the output must be that key's latent, whether the key sits at position 0, at either side of a page
+    border, at either side of a key-tile border or is the very last visible one, for a decoding token (with and
+    without key splits) and for the last token of a prompt portion."""
+    from llmctl_b200.ops import latent_attention as L
+    from llmctl_b200.serve.ragged import Portion, RaggedBatch
+    dt = torch.float32 if kind == "fp32" else torch.bfloat16
+    H, R, dr, dn, bs, n = (3, 64, 64, 8, 64, 700) if kind != "fp32" else (3, 24, 8, 8, 16, 700)
+    rows = {"fp32": 16, "bf16_rows16": 16, "bf16_rows32": 32, "bf16_tcgen05": 128}[kind]
+    if rows == 128:
+        assert L.uses_tcgen05(dt, R, dr, bs, True)
+    g = torch.Generator().manual_seed(4)
+    f = torch.ones(dr // 2)
+    nb = (n + bs - 1) // bs + 2
+    table = torch.randperm(nb, generator=g).tolist()[:(n + bs - 1) // bs]
+    base = torch.randn(n, R + dr, generator=g) * 0.1
+    slots = torch.tensor([table[j // bs] * bs + j % bs for j in range(n)])
+    for far in (0, 31, 32, 63, 64, 65, 383, 384, 640, n - 1):
+        r = base.clone()
+        r[far] = 0
+        r[far, 0] = 8.0
+        cache = torch.zeros(nb, bs, R + dr)
+        cache.view(-1, R + dr)[slots] = r
+        cache = cache.to(dt).cuda()
+        for ntok, splits in ((1, 1), (1, 4), (40, 1)):
+            start = n - ntok
+            if far >= start and ntok > 1:
+                continue
+            b = RaggedBatch([Portion(1, [0] * ntok, start, [], table)], bs, torch.device("cuda"))
+            ql = torch.zeros(ntok, H, R)
+            ql[:, :, 0] = 8.0
+            q = torch.zeros(ntok, H * (dn + dr)).to(dt).cuda()
+            qlg = (ql.to(dt) if dt == torch.bfloat16 else ql).cuda()
+            use = rows if (rows != 32 or ntok > 1) else 16
+            out = L.latent_attention(qlg, q, dn, cache, b.block_tables, b.tiles(use), b.positions, f.cuda(), 1.0, 1.0,
+                                     b.heads_per_tile(H, use), n, splits, rows=use)
+            torch.cuda.synchronize()
+            want = r[far, :R].to(dt).float()
+            got = out[-1].float().cpu()
+            assert torch.allclose(got, want.expand(H, R), atol=2e-2), f"{kind}: far key at {far}, {ntok} tokens, {splits} splits"
+    if rows == 128:
+        assert L.tcgen05_status() == 0
+
+
 @pytest.mark.parametrize("dt", DTYPES)
 @pytest.mark.parametrize("T,E,top,scale_input", [(70, 5, 2, True), (3, 8, 1, True), (200, 3, 3, False), (700, 6, 2, True)])
 def test_moe_kernels(cuda_device, dt, T, E, top, scale_input):
