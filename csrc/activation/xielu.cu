@@ -5,6 +5,7 @@
 //                  (the caller passes a_pos and a_neg; they depend on two learned numbers only)
 //   gated SiLU   : out = silu(gate) * up on a packed [rows, 2F] activation (gate first) of either type
 //                  (csrc/swiglu/swiglu.cu is the bf16-only training kernel with a backward).
+//   squared ReLU : max(z, 0)^2
 // Reference: none (the reference has no model code).
 #include "../common/dtype.cuh"
 
@@ -34,6 +35,15 @@ gated_silu_kernel(const T* __restrict__ gu, long long ld, T* __restrict__ out, i
   }
 }
 
+template <typename T>
+__global__ void __launch_bounds__(256) relu_squared_kernel(const T* __restrict__ z, T* __restrict__ out, long long n) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float v = fmaxf(to_f32(z[i]), 0.f);
+    out[i] = from_f32<T>(v * v);
+  }
+}
+
 static inline int grid_for(long long n) {
   long long b = (n + 255) / 256;
   if (b > kNumSMs * 16) b = kNumSMs * 16;
@@ -57,5 +67,12 @@ LLMCTL_API int llmctl_gated_silu(const void* gate_up, long long ld, void* out, i
   if (rows == 0 || F == 0) return 0;
   LLMCTL_DISPATCH_DTYPE(is_fp32, T, (gated_silu_kernel<T><<<grid_for(static_cast<long long>(rows) * F), 256, 0, (cudaStream_t)stream>>>(
                                         (const T*)gate_up, ld, (T*)out, rows, F)));
+  LLMCTL_RETURN_LAST();
+}
+
+LLMCTL_API int llmctl_relu_squared(const void* z, void* out, int is_fp32, long long n, void* stream) {
+  LLMCTL_BEGIN();
+  if (n == 0) return 0;
+  LLMCTL_DISPATCH_DTYPE(is_fp32, T, (relu_squared_kernel<T><<<grid_for(n), 256, 0, (cudaStream_t)stream>>>((const T*)z, (T*)out, n)));
   LLMCTL_RETURN_LAST();
 }

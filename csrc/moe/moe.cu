@@ -58,7 +58,9 @@ moe_route_kernel(const float* __restrict__ x, const T* __restrict__ wr, const T*
   }
   __syncthreads();
   if (threadIdx.x == 0) {
-    if (softmax_scores) {
+    if (softmax_scores == 2) {
+      // raw logits decide the choice; the weights are a softmax over the chosen logits only (below)
+    } else if (softmax_scores) {
       float m = -INFINITY, z = 0.f;
       for (int e = 0; e < E; ++e) m = fmaxf(m, score[e]);
       for (int e = 0; e < E; ++e) z += (score[e] = expf(score[e] - m));
@@ -81,7 +83,12 @@ moe_route_kernel(const float* __restrict__ x, const T* __restrict__ wr, const T*
       score[best] = -INFINITY;
       atomicAdd(&counts[best], 1);
     }
-    if (renormalise)
+    if (softmax_scores == 2) {
+      const float m = weights[tok * top];        // the first choice is the largest logit
+      float z = 0.f;
+      for (int k = 0; k < top; ++k) z += (weights[tok * top + k] = expf(weights[tok * top + k] - m));
+      for (int k = 0; k < top; ++k) weights[tok * top + k] /= z;
+    } else if (renormalise)
       for (int k = 0; k < top; ++k) weights[tok * top + k] /= total;
   }
 }

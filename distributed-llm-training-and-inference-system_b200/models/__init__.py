@@ -1,2 +1,3 @@
 """Model families.  Importing the package registers every architecture (``models/registry.py``)."""
 from . import nafazen as _nafazen  # noqa: F401  (registers "Nafazen")
+from . import teluzen as _teluzen  # noqa: F401  (registers "Teluzen")

@@ -1,5 +1,5 @@
-"""Feed-forward layers for inference batches: a two-matrix MLP with the xIELU activation and a sigmoid-routed
-mixture of gated experts with an optional gated shared expert.
+"""Feed-forward layers for inference batches: two-matrix MLPs with the xIELU or the squared-ReLU activation and a
+routed mixture of gated experts (sigmoid, softmax or chosen-logit softmax weights) with an optional shared expert.
 
 Reference: none — the reference has no model code (reference llmctl/runtime/engine.py:119-140)."""
 from __future__ import annotations
@@ -37,9 +37,27 @@ class XieluMLP(nn.Module):
         return ops.linear(eops.xielu(ops.linear(h, self.up), *self._coef), self.down)
 
 
+class SquaredReluMLP(nn.Module):
+    """``Wdown relu(Wup h)^2``."""
+
+    def __init__(self, width: int, ff: int, dtype, device):
+        super().__init__()
+        self.up = nn.Parameter(torch.empty(ff, width, dtype=dtype, device=device))
+        self.down = nn.Parameter(torch.empty(width, ff, dtype=dtype, device=device))
+
+    def load(self, get, prefix: str) -> None:
+        with torch.no_grad():
+            self.up.copy_(get(prefix + "up"))
+            self.down.copy_(get(prefix + "down"))
+
+    def forward(self, h: torch.Tensor, x32: torch.Tensor) -> torch.Tensor:
+        return ops.linear(eops.relu_squared(ops.linear(h, self.up)), self.down)
+
+
 class GatedExpertMoE(nn.Module):
-    """``top`` of ``experts`` gated-SiLU experts per token.  Scores are sigmoids of fp32 router logits (or a softmax,
-    ``softmax_scores``), optionally renormalised over the chosen ones; the score multiplies the expert's input
+    """``top`` of ``experts`` gated-SiLU experts per token.  Scores are sigmoids of fp32 router logits (or a softmax over
+    all experts, ``softmax_scores`` True; or, ``softmax_scores`` 2, the largest logits are chosen and weighted by a
+    softmax over the chosen logits only), optionally renormalised over the chosen ones; the score multiplies the expert's input
     (``scale_input``) or its output.  A shared expert of its own size runs for every token, times sigmoid(wg . h)
     when ``shared_gate``."""
 
@@ -69,7 +87,8 @@ class GatedExpertMoE(nn.Module):
                 self.shared_gate.copy_(get(prefix + "shared.sg").reshape(-1))
 
     def forward(self, h: torch.Tensor, x32: torch.Tensor) -> torch.Tensor:
-        """h: the stream in the activation type, x32: the fp32 stream.  Returns fp32 [T, W]."""
+        """h: the layer's input in the activation type, x32: the same in fp32 (what the router and the experts read).
+        Returns fp32 [T, W]."""
         shared = None
         if self.shared_gate_up is not None:
             shared = ops.linear(eops.gated_silu(ops.linear(h, self.shared_gate_up)), self.shared_down)

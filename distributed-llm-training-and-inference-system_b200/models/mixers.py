@@ -12,6 +12,19 @@ single rotated key part shared by all heads.  Queries go through their own norme
     ol       = attention over the cache rows (ops.latent_attention.latent_attention)   [T, H, R]
     out      = (ol Uv_h^T) Wo^T
 
+``PooledWindowAttention``: grouped-query attention over a sliding window of ``window`` tokens plus one pooled key/value
+(the mean of the cached keys / values) per block of ``pool`` tokens that lies wholly before the window.  Optional parts,
+each a field of ``PooledWindowAttentionSpec``: projection biases, an RMS norm over the whole q and the whole k
+projection, rotation of the first ``rot_dims`` numbers of every head (plain or YaRN-blended spectrum), a learned score
+temperature per head, mixing of the normalised attention weights across heads by a learned [H, H] matrix, and mixing of
+the layer's values with the values the first such layer computed for the same token.  Per step:
+
+    qkv      = h Wqkv^T                         (one packed GEMM)
+    q, cache = bias / norm / rotate / value mix / append     (ops.window_attention.window_qkv_write)
+    pooled rows of the blocks the step completes             (ops.window_attention.window_pool_update)
+    o        = attention over window + pooled rows           (ops.window_attention.pooled_window_attention)
+    out      = o Wo^T
+
 Reference: none — the reference has no model code (reference llmctl/runtime/engine.py:119-140)."""
 from __future__ import annotations
 
@@ -23,6 +36,7 @@ import torch.nn as nn
 
 from ..ops import functional as ops
 from ..ops import latent_attention as lops
+from ..ops import window_attention as wops
 from ..ops.elementwise import rope_frequencies
 
 
@@ -106,3 +120,97 @@ class LatentAttention(nn.Module):
                                    batch.attention_splits(s.heads, rows), rows=rows)
         o = torch.bmm(ol.transpose(0, 1), self.w_uv.transpose(1, 2)).transpose(0, 1).reshape(T, s.heads * s.vdim)
         return ops.linear(o, self.w_o)
+
+
+@dataclass
+class PooledWindowAttentionSpec:
+    heads: int
+    kv_heads: int
+    dim: int            # query/key size per head
+    vdim: int           # value size per head
+    scale: float
+    window: int = 0     # 0: every earlier token is seen, nothing is pooled
+    pool: int = 0       # tokens per pooled block
+    rot_dims: int = 0   # rotated numbers per head (even, <= dim); 0: no rotation
+    rot_base: float = 10000.0
+    rot_scaling: Optional[Dict[str, Any]] = None
+    bias: bool = True
+    qk_norm: bool = True            # RMS norm over the whole q / k projection, per-coordinate weights
+    head_temperature: bool = True   # scores of head h are multiplied by a learned number
+    talking_heads: bool = True      # normalised weights are mixed across heads by a learned [H, H] matrix
+    v_mix: bool = False             # values are blended with those of the first v_mix layer
+
+    @property
+    def cache_width(self) -> int:
+        return self.kv_heads * (self.dim + self.vdim)
+
+    def rows_per_page(self, block_size: int) -> int:
+        return block_size + wops.pooled_rows_per_page(block_size, self.pool if self.window else 0)
+
+
+class PooledWindowAttention(nn.Module):
+    TILE_TOKENS = 16        # tile width of the ragged batch this mixer asks for (serve/ragged.py)
+
+    def __init__(self, width: int, spec: PooledWindowAttentionSpec, eps: float, dtype, device):
+        super().__init__()
+        s = self.spec = spec
+        if s.heads % s.kv_heads or s.rot_dims % 2 or s.rot_dims > s.dim or (s.window and s.pool < 1):
+            raise ValueError(f"inconsistent attention sizes: {s}")
+        self.eps = eps
+        kw = dict(dtype=dtype, device=device)
+        f32 = dict(dtype=torch.float32, device=device)
+        nq, nk, nv = s.heads * s.dim, s.kv_heads * s.dim, s.kv_heads * s.vdim
+        self.w_qkv = nn.Parameter(torch.empty(nq + nk + nv, width, **kw))               # [q ; k ; v]
+        self.b_qkv = nn.Parameter(torch.zeros(nq + nk + nv, **kw)) if s.bias else None
+        self.q_norm = nn.Parameter(torch.ones(nq, **f32)) if s.qk_norm else None
+        self.k_norm = nn.Parameter(torch.ones(nk, **f32)) if s.qk_norm else None
+        self.temp = nn.Parameter(torch.ones(s.heads, **f32)) if s.head_temperature else None
+        self.talk = nn.Parameter(torch.eye(s.heads, **f32)) if s.talking_heads else None
+        self.vmix = nn.Parameter(torch.zeros(1, **f32)) if s.v_mix else None
+        self.w_o = nn.Parameter(torch.empty(width, s.heads * s.vdim, **kw))
+        if s.rot_dims:
+            f, self.rot_mult = rope_frequencies(s.rot_dims, s.rot_base, s.rot_scaling)
+        else:
+            f, self.rot_mult = torch.zeros(1), 1.0
+        self.register_buffer("rot_freq", f.to(device), persistent=False)
+
+    def load(self, get, prefix: str) -> None:
+        """Checkpoint names under ``prefix``: q, k, v (+ ``.b`` biases, ``q.norm`` / ``k.norm``), temp, talk, vmix, o."""
+        s = self.spec
+        with torch.no_grad():
+            self.w_qkv.copy_(torch.cat([get(prefix + "q"), get(prefix + "k"), get(prefix + "v")], dim=0))
+            if s.bias:
+                self.b_qkv.copy_(torch.cat([get(prefix + "q.b"), get(prefix + "k.b"), get(prefix + "v.b")], dim=0))
+            if s.qk_norm:
+                self.q_norm.copy_(get(prefix + "q.norm").float())
+                self.k_norm.copy_(get(prefix + "k.norm").float())
+            if s.head_temperature:
+                self.temp.copy_(get(prefix + "temp").float())
+            if s.talking_heads:
+                self.talk.copy_(get(prefix + "talk").float())
+            if s.v_mix:
+                self.vmix.copy_(get(prefix + "vmix").float().reshape(1))
+            self.w_o.copy_(get(prefix + "o"))
+
+    def forward(self, h: torch.Tensor, batch, cache: torch.Tensor, v_first: Optional[torch.Tensor] = None):
+        """h: [T, W] in the activation type; ``cache``: this layer's [pages, bs + PS, G (d + e)].  ``v_first``: the values
+        of the first v_mix layer for the step's tokens (None in that layer itself, which then returns them).  Returns
+        (output [T, W], v_first)."""
+        s = self.spec
+        T = h.shape[0]
+        bs = batch.block_size
+        qkv = ops.linear(h, self.w_qkv)
+        v_mode = 0
+        if s.v_mix:
+            v_mode = 2 if v_first is not None else 1
+            if v_first is None:
+                v_first = torch.empty(T, s.kv_heads * s.vdim, dtype=h.dtype, device=h.device)
+        q = wops.window_qkv_write(qkv, self.b_qkv, self.q_norm, self.k_norm, s.heads, s.kv_heads, s.dim, s.vdim, s.rot_dims,
+                                  self.rot_freq, self.rot_mult, self.eps, batch.positions, batch.slots, cache, bs,
+                                  v_first if v_mode else None, v_mode, self.vmix)
+        pool = s.pool if s.window else 0
+        wops.window_pool_update(cache, batch.positions, batch.slots, batch.seq_rows, batch.block_tables, bs, pool)
+        o = wops.pooled_window_attention(q, cache, batch.block_tables, batch.tiles(self.TILE_TOKENS),
+                                         1 if batch.decode_only else self.TILE_TOKENS, batch.positions, self.temp, self.talk,
+                                         s.scale, s.heads, s.kv_heads, s.dim, s.vdim, s.window, pool, bs, h.dtype)
+        return ops.linear(o, self.w_o), v_first

@@ -1,8 +1,10 @@
 """Inference-side elementwise / normalisation ops that exist for bf16 AND fp32 activations: post-norm residual
 update with a single gain, scalar-gain RMS norm of selected rows, scaled embedding lookup, logit soft-capping, xIELU
-and gated SiLU, plus the frequency spectrum of interleaved-pair rotary embeddings (plain or YaRN-blended).
-CUDA tensors run the kernels in csrc/norm/scalar_rmsnorm.cu and csrc/activation/xielu.cu; CPU tensors run the
-PyTorch restatement below (CPU tests).  Sums, gains and the residual stream are fp32 in both.
+and gated SiLU, plus the frequency spectrum of interleaved-pair rotary embeddings (plain or YaRN-blended); for the
+sandwich layout (a weighted RMS norm before and after every sublayer): embedding plus learned position vector,
+weighted RMS norm of rows, fused out-norm + residual + next in-norm, and the squared ReLU.
+CUDA tensors run the kernels in csrc/norm/scalar_rmsnorm.cu, csrc/norm/sandwich_norm.cu and csrc/activation/xielu.cu;
+CPU tensors run the PyTorch restatement below (CPU tests).  Sums, gains and the residual stream are fp32 in both.
 
 Reference: none — the reference has no model code (reference llmctl/runtime/engine.py:119-140 loads HF models)."""
 from __future__ import annotations
@@ -22,6 +24,11 @@ native.register_signature("llmctl_embed_scale", [c_void_p, c_void_p, c_int, c_fl
 native.register_signature("llmctl_softcap", [c_void_p, c_ll, c_float, c_void_p])
 native.register_signature("llmctl_xielu", [c_void_p, c_void_p, c_int, c_ll, c_float, c_float, c_void_p])
 native.register_signature("llmctl_gated_silu", [c_void_p, c_ll, c_void_p, c_int, c_int, c_int, c_void_p])
+native.register_signature("llmctl_relu_squared", [c_void_p, c_void_p, c_int, c_ll, c_void_p])
+native.register_signature("llmctl_embed_positions", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p])
+native.register_signature("llmctl_rmsnorm_rows", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+native.register_signature("llmctl_sandwich_residual", [c_void_p, c_int, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                                        c_float, c_void_p])
 
 
 def _is32(t: torch.Tensor) -> int:
@@ -139,3 +146,55 @@ def gated_silu(gate_up: torch.Tensor) -> torch.Tensor:
         return out
     g, u = gate_up.float().chunk(2, dim=-1)
     return (F.silu(g) * u).to(gate_up.dtype)
+
+
+def relu_squared(z: torch.Tensor) -> torch.Tensor:
+    """``max(z, 0)^2``, evaluated in fp32, in z's type."""
+    if z.is_cuda:
+        z = z.contiguous()
+        out = torch.empty_like(z)
+        native.call("llmctl_relu_squared", z.data_ptr(), out.data_ptr(), _is32(z), z.numel(), native.stream_ptr())
+        return out
+    return torch.relu(z.float()).pow(2).to(z.dtype)
+
+
+def embed_positions(tokens: torch.Tensor, positions: torch.Tensor, table: torch.Tensor, pos_table: torch.Tensor) -> torch.Tensor:
+    """``x[t] = table[tokens[t]] + pos_table[positions[t]]`` -> the fp32 residual stream [T, W]."""
+    T, W = tokens.numel(), table.shape[1]
+    if table.is_cuda:
+        x = torch.empty(T, W, dtype=torch.float32, device=table.device)
+        native.call("llmctl_embed_positions", tokens.data_ptr(), positions.data_ptr(), table.data_ptr(), pos_table.data_ptr(),
+                    _is32(table), x.data_ptr(), T, W, native.stream_ptr())
+        return x
+    return table[tokens.reshape(-1)].float() + pos_table[positions.reshape(-1).long()].float()
+
+
+def rmsnorm_rows(x: torch.Tensor, rows: Optional[torch.Tensor], w: torch.Tensor, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """``w * x[rows] / rms(x[rows])`` of the fp32 stream (all rows when ``rows`` is None) in ``out_dtype``; w: fp32 [W]."""
+    n = x.shape[0] if rows is None else rows.numel()
+    assert x.dtype == torch.float32 and w.dtype == torch.float32
+    if x.is_cuda:
+        out = torch.empty(n, x.shape[1], dtype=out_dtype, device=x.device)
+        native.call("llmctl_rmsnorm_rows", x.data_ptr(), native.ptr(rows), w.data_ptr(), out.data_ptr(), int(out_dtype == torch.float32),
+                    n, x.shape[1], float(eps), native.stream_ptr())
+        return out
+    xs = x if rows is None else x[rows]
+    return (xs / torch.sqrt(xs.pow(2).mean(-1, keepdim=True) + eps) * w).to(out_dtype)
+
+
+def sandwich_residual(y: torch.Tensor, x: torch.Tensor, w_out: torch.Tensor, w_next: Optional[torch.Tensor], eps: float,
+                      act_dtype: torch.dtype) -> Optional[torch.Tensor]:
+    """``x += w_out * y / rms(y)`` in place on the fp32 stream; with ``w_next`` also returns ``w_next * x / rms(x)`` of the
+    new stream in ``act_dtype`` (the next sublayer's input) from the same pass.  Weights: fp32 [W]."""
+    T, W = x.shape
+    assert x.dtype == torch.float32 and x.is_contiguous() and y.shape == x.shape and y.stride(1) == 1
+    if x.is_cuda:
+        out = torch.empty(T, W, dtype=act_dtype, device=x.device) if w_next is not None else None
+        native.call("llmctl_sandwich_residual", y.data_ptr(), _is32(y), y.stride(0), x.data_ptr(), w_out.data_ptr(), native.ptr(w_next),
+                    native.ptr(out), int(act_dtype == torch.float32), T, W, float(eps), native.stream_ptr())
+        return out
+    yf = y.float()
+    x += yf / torch.sqrt(yf.pow(2).mean(-1, keepdim=True) + eps) * w_out
+    if w_next is None:
+        return None
+    return (x / torch.sqrt(x.pow(2).mean(-1, keepdim=True) + eps) * w_next).to(act_dtype)

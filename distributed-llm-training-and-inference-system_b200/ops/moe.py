@@ -37,7 +37,9 @@ def uses_tcgen05(act_dtype: torch.dtype, W: int, F: int) -> bool:
 
 def route(x: torch.Tensor, w_router: torch.Tensor, top: int, w_gate: Optional[torch.Tensor] = None, softmax: bool = False,
           renormalise: bool = False):
-    """x: fp32 [T, W].  Returns (ids int32 [T, top], weights fp32 [T, top], gate fp32 [T] or None, counts int32 [E])."""
+    """x: fp32 [T, W].  ``softmax``: False = sigmoid scores, True = softmax over all experts, 2 = the largest raw logits
+    are chosen and the weights are a softmax over the chosen logits only.
+    Returns (ids int32 [T, top], weights fp32 [T, top], gate fp32 [T] or None, counts int32 [E])."""
     T, W = x.shape
     E = w_router.shape[0]
     if x.is_cuda:
@@ -50,9 +52,11 @@ def route(x: torch.Tensor, w_router: torch.Tensor, top: int, w_gate: Optional[to
                     native.stream_ptr())
         return ids, wts, gate, counts
     z = x @ w_router.float().t()
-    s = torch.softmax(z, -1) if softmax else torch.sigmoid(z)
+    s = z if int(softmax) == 2 else torch.softmax(z, -1) if softmax else torch.sigmoid(z)
     wts, ids = torch.topk(s, top, dim=-1)
-    if renormalise:
+    if int(softmax) == 2:
+        wts = torch.softmax(wts, -1)
+    elif renormalise:
         wts = wts / wts.sum(-1, keepdim=True)
     gate = torch.sigmoid(x @ w_gate.float().reshape(-1)) if w_gate is not None else None
     return ids.to(torch.int32), wts, gate, torch.bincount(ids.reshape(-1), minlength=E).to(torch.int32)

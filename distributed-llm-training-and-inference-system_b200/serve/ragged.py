@@ -54,13 +54,14 @@ class RaggedBatch:
             n_out = sum(len(p.want) for p in portions)
             ntiles = tuple(sum((len(p.tokens) + w - 1) // w for p in portions) for w in self._tile_tokens)
         # int32 words: tokens(2T) | slots(2T) | out_rows(2 n_out) | positions(T) | block tables(B max_blocks) | tiles(4 n) per width
-        sizes = [2 * T, 2 * T, 2 * n_out, T, B * max_blocks] + [4 * n for n in ntiles]
+        # | block-table row of every token(T)
+        sizes = [2 * T, 2 * T, 2 * n_out, T, B * max_blocks] + [4 * n for n in ntiles] + [T]
         offs = np.concatenate([[0], np.cumsum(sizes)])
         self._host = torch.zeros(int(offs[-1]), dtype=torch.int32, pin_memory=device.type == "cuda")
         a = self._host.numpy()
         self._h = (a[offs[0]:offs[1]].view(np.int64), a[offs[1]:offs[2]].view(np.int64), a[offs[2]:offs[3]].view(np.int64),
                    a[offs[3]:offs[4]], tuple(a[offs[5 + k]:offs[6 + k]].reshape(n, 4) for k, n in enumerate(ntiles)),
-                   a[offs[4]:offs[5]].reshape(B, max_blocks))
+                   a[offs[4]:offs[5]].reshape(B, max_blocks), a[offs[5 + len(ntiles)]:offs[6 + len(ntiles)]])
         dev = torch.empty_like(self._host, device=device) if device.type == "cuda" else self._host
         self._dev = dev
         self.nbytes = self._host.numel() * 4
@@ -71,11 +72,12 @@ class RaggedBatch:
         self.positions = dev[offs[3]:offs[4]]
         self._tiles = {w: dev[offs[5 + k]:offs[6 + k]].view(ntiles[k], 4) for k, w in enumerate(TILE_WIDTHS)}
         self.block_tables = dev[offs[4]:offs[5]].view(B, max_blocks)
+        self.seq_rows = dev[offs[5 + len(ntiles)]:offs[6 + len(ntiles)]]       # int32 [T]: row of block_tables per token
         self.refill(portions)
 
     def refill(self, portions: List[Portion]) -> None:
         """Write the description of ``portions`` into the (same) buffers and copy it to the device."""
-        tokens, slots, out_rows, positions, tiles, tables = self._h
+        tokens, slots, out_rows, positions, tiles, tables, seq_rows = self._h
         block_size = self.block_size
         if self.pad_to is not None:
             assert len(portions) <= self.pad_to[0] and all(len(p.tokens) == 1 for p in portions)
@@ -83,6 +85,7 @@ class RaggedBatch:
             slots[:] = -1
             positions[:] = 0
             tables[:] = 0
+            seq_rows[:] = np.arange(self.pad_to[0])
             for r in range(self.pad_to[0]):                 # padding rows too: one tile and one (ignored) logits row each
                 for tl in tiles:
                     tl[r] = (r, 1, r, 0)
@@ -99,6 +102,7 @@ class RaggedBatch:
             positions[t:t + n] = pos
             slots[t:t + n] = bt[pos // block_size] * block_size + pos % block_size
             tables[b, :len(bt)] = bt
+            seq_rows[t:t + n] = b
             if self.pad_to is None:
                 for w in p.want:
                     assert 0 <= w < n

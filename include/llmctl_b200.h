@@ -260,6 +260,35 @@ int llmctl_moe_combine(const void* expert_out, int W, const int* pair_row, const
                        int scale_output, const void* shared_out, const float* gate, float* y, int tokens, int is_fp32,
                        void* stream);
 
+/* ---- sandwich-norm layout and pooled-window attention (csrc/norm/sandwich_norm.cu, csrc/activation/xielu.cu,
+ *      csrc/attention/pooled_window_attention.cu) ---- */
+int llmctl_relu_squared(const void* z, void* out, int is_fp32, long long n, void* stream);
+/* x[t] = table[tokens[t]] + pos_table[positions[t]] in fp32. */
+int llmctl_embed_positions(const long long* tokens, const int* positions, const void* table, const void* pos_table,
+                           int is_fp32, float* x, int rows, int cols, void* stream);
+/* out[r] = w * x[rows[r]] / rms(x[rows[r]]); rows may be null (rows 0..n_out-1); x and w fp32. */
+int llmctl_rmsnorm_rows(const float* x, const long long* rows, const float* w, void* out, int out_fp32, int n_out, int cols,
+                        float eps, void* stream);
+/* x += wb * y / rms(y) on the fp32 stream; with w_next also out = w_next * x / rms(x) of the new stream. */
+int llmctl_sandwich_residual(const void* y, int y_fp32, long long ldy, float* x, const float* wb, const float* w_next,
+                             void* out, int out_fp32, int rows, int cols, float eps, void* stream);
+/* Packed projection [q | k | v] -> fp32 queries and the token's cache row: bias, RMS norm over the whole q / k
+ * projection, rotation of the first `rot` numbers of every head, value mixing (v_mode 1: publish v_first, 2: blend). */
+int llmctl_window_qkv_write(const void* qkv, long long ld, const void* bias, const float* qn_w, const float* kn_w, int H,
+                            int G, int d, int e, int rot, const float* freq, float mult, float eps, const int* positions,
+                            const long long* slots, float* q_out, void* cache, int bs, int PS, void* v_first, int v_mode,
+                            const float* lam, int tokens, int is_fp32, void* stream);
+/* Pooled rows (means of P cached rows) of the blocks that the step's tokens complete. */
+int llmctl_window_pool_update(void* cache, const int* positions, const long long* slots, const int* seq_rows,
+                              const int* block_tables, int max_blocks, int bs, int PS, int P, int Wc, int tokens,
+                              int is_fp32, void* stream);
+int llmctl_pooled_window_attention_rows(int H, int d, int e, int tile_tokens);
+/* Attention over a window of S tokens and the pooled rows of the blocks before it; temp / talk may be null. */
+int llmctl_pooled_window_attention(const float* q, const void* cache, const int* block_tables, int max_blocks,
+                                   const int* tiles, int ntiles, int tile_tokens, const int* positions, const float* temp,
+                                   const float* talk, float scale, int H, int G, int d, int e, int S, int P, int bs, int PS,
+                                   void* out, int is_fp32, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
