@@ -88,24 +88,33 @@ def attention_mixer(h: torch.Tensor, positions: torch.Tensor, m: dict, t: Dict[s
     if m.get("v_mix") and v_first is not None:
         lam = t[pre + "vmix"].reshape(())
         v = (1 - lam) * v + lam * v_first
-    k, v = cache_round(k), cache_round(v)
     mask = m.get("mask")
     S, P = (mask["size"], mask["pool"]) if mask else (None, None)
+    o = attend(q, cache_round(k), cache_round(v), S, P, m["scale"], t[pre + "temp"], t[pre + "talk"], cache_round)
+    return o.reshape(T, H * e) @ t[pre + "o"].T, v, v_own
+
+
+def attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, S: Optional[int], P: Optional[int], scale: float,
+           temp: Optional[torch.Tensor], talk: Optional[torch.Tensor], cache_round: Callable = lambda z: z) -> torch.Tensor:
+    """q: [T, H, d], k: [T, G, d], v: [T, G, e] of one sequence from position 0 -> [T, H, e]."""
+    T, H = q.shape[0], q.shape[1]
+    rep = H // k.shape[1]
     tok, blk = visibility(T, S, P)
     keys, vals, vis = k, v, tok
     if S is not None and T // P > 0:
         keys = torch.cat([cache_round(pooled(k, P)), k], 0)
         vals = torch.cat([cache_round(pooled(v, P)), v], 0)
         vis = torch.cat([blk, tok], 1)
-    rep = H // G
     kh = keys.repeat_interleave(rep, dim=1)                                  # [N, H, d]
-    s = torch.einsum("thd,nhd->htn", q, kh) * m["scale"] * t[pre + "temp"][:, None, None]
+    s = torch.einsum("thd,nhd->htn", q, kh) * scale
+    if temp is not None:
+        s = s * temp[:, None, None]
     s = s.masked_fill(~vis[None], float("-inf"))
     w = torch.softmax(s, -1)
-    w = torch.einsum("hg,gtn->htn", t[pre + "talk"], w)
+    if talk is not None:
+        w = torch.einsum("hg,gtn->htn", talk, w)
     vh = vals.repeat_interleave(rep, dim=1)                                  # [N, H, e]
-    o = torch.einsum("htn,nhe->the", w, vh).reshape(T, H * e)
-    return o @ t[pre + "o"].T, v, v_own
+    return torch.einsum("htn,nhe->the", w, vh)
 
 
 def dense_ff(h: torch.Tensor, t: Dict[str, torch.Tensor], pre: str) -> torch.Tensor:
@@ -158,3 +167,54 @@ def forward(cfg: dict, tensors: Dict[str, torch.Tensor], tokens: List[int], cach
             x = x + rms_norm(y, t[p + "norm2b"], eps)
         trace.append(x.clone())
     return rms_norm(x, t["final.norm"], eps) @ t["head"].T, trace
+
+
+def random_weights(cfg: dict, seed: int = 0) -> Dict[str, torch.Tensor]:
+    """Random tensors under the checkpoint names, fp32 values that bfloat16 holds exactly."""
+    g = torch.Generator().manual_seed(seed)
+    W = cfg["width"]
+    t: Dict[str, torch.Tensor] = {}
+
+    def mat(name, out, inp, gain=1.0):
+        t[name] = torch.randn(out, inp, generator=g) * gain / inp ** 0.5
+
+    def vec(name, n, mean=1.0, std=0.2):
+        t[name] = mean + std * torch.randn(n, generator=g)
+    t["embed"] = torch.randn(cfg["vocab"], W, generator=g)
+    t["pos"] = 0.5 * torch.randn(cfg["max_positions"], W, generator=g)
+    mat("head", cfg["vocab"], W)
+    vec("final.norm", W)
+    for i, layer in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", layer["mixer"]
+        H, G, d, e = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        for n in ("norm1", "norm1b"):
+            vec(p + n, W)
+        mat(p + "mix.q", H * d, W, 2.0)
+        mat(p + "mix.k", G * d, W, 2.0)
+        mat(p + "mix.v", G * e, W)
+        vec(p + "mix.q.b", H * d, 0.0, 0.3)
+        vec(p + "mix.k.b", G * d, 0.0, 0.3)
+        vec(p + "mix.v.b", G * e, 0.0, 0.3)
+        vec(p + "mix.q.norm", H * d)
+        vec(p + "mix.k.norm", G * d)
+        vec(p + "mix.temp", H, 1.0, 0.3)
+        t[p + "mix.talk"] = torch.eye(H) + 0.3 * torch.randn(H, H, generator=g)
+        t[p + "mix.vmix"] = torch.tensor(0.35) + 0.1 * torch.randn((), generator=g)
+        mat(p + "mix.o", W, H * e)
+        mlp = layer.get("mlp")
+        if not mlp:
+            continue
+        for n in ("norm2", "norm2b"):
+            vec(p + n, W)
+        if mlp["kind"] == "dense":
+            mat(p + "mlp.up", mlp["ff"], W)
+            mat(p + "mlp.down", W, mlp["ff"])
+            continue
+        names = [f"e{k}." for k in range(mlp["router"]["experts"])] + (["shared."] if mlp.get("shared") else [])
+        for n in names:
+            ff = mlp["shared"]["ff"] if n == "shared." else mlp["expert"]["ff"]
+            mat(p + "mlp." + n + "gate", ff, W)
+            mat(p + "mlp." + n + "up", ff, W)
+            mat(p + "mlp." + n + "down", W, ff)
+        mat(p + "mlp.router", mlp["router"]["experts"], W, 3.0)
+    return {k: v.to(torch.bfloat16).to(torch.float32) for k, v in t.items()}

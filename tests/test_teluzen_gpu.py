@@ -1,0 +1,266 @@
+"""Teluzen on a B200: every new kernel against the plain oracle or the PyTorch restatement of the same op (bf16 and
+fp32), then the served model against the oracle: whole prompts, decoding through the cache, portions and mixed batches,
+in fp32 (tight) and bf16, and greedy generation with the decode step replayed as a CUDA graph."""
+import copy
+
+import pytest
+import torch
+
+import teluzen_oracle as oracle
+from test_teluzen_cpu import _decisive, make_engine, ref_logits, small_cfg
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dt):
+    return 3e-5 if dt == torch.float32 else 2e-2
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+def test_sandwich_norm_kernels(cuda_device, dt):
+    from llmctl_b200.ops import elementwise as E
+    torch.manual_seed(0)
+    for T, Wd in ((5, 48), (33, 1000), (2, 4096)):
+        y, x = torch.randn(T, Wd).to(dt), torch.randn(T, Wd)
+        wb, wn = torch.rand(Wd) + 0.5, torch.rand(Wd) + 0.5
+        xr = x.clone()
+        hr = E.sandwich_residual(y, xr, wb, wn, 1e-5, dt)
+        xg = x.cuda()
+        hg = E.sandwich_residual(y.cuda(), xg, wb.cuda(), wn.cuda(), 1e-5, dt)
+        assert torch.allclose(xg.cpu(), xr, atol=1e-5) and torch.allclose(hg.float().cpu(), hr.float(), atol=tol(dt) * 4)
+        rows = torch.tensor([T - 1, 0])
+        a = E.rmsnorm_rows(xg, rows.cuda(), wn.cuda(), 1e-5, dt)
+        assert torch.allclose(a.float().cpu(), E.rmsnorm_rows(xr, rows, wn, 1e-5, dt).float(), atol=tol(dt) * 4)
+        z = torch.randn(T, Wd).to(dt)
+        assert torch.equal(E.relu_squared(z.cuda()).cpu(), E.relu_squared(z))
+    table, pos = torch.randn(9, 40).to(dt), torch.randn(30, 40).to(dt)
+    tk, ps = torch.tensor([3, 3, 8]), torch.tensor([0, 29, 5], dtype=torch.int32)
+    assert torch.equal(E.embed_positions(tk.cuda(), ps.cuda(), table.cuda(), pos.cuda()).cpu(), E.embed_positions(tk, ps, table, pos))
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("H,G,d,e,rot", [(4, 2, 8, 6, 4), (3, 3, 6, 6, 6), (6, 1, 4, 10, 0), (16, 4, 128, 128, 64), (5, 5, 33, 7, 32)])
+def test_projection_postprocessing_kernel(cuda_device, dt, H, G, d, e, rot):
+    from llmctl_b200.ops import window_attention as W
+    from llmctl_b200.ops.elementwise import rope_frequencies
+    torch.manual_seed(1)
+    T, bs, P = 9, 4, 3
+    PS = W.pooled_rows_per_page(bs, P)
+    N = (H + G) * d + G * e
+    qkv, bias = torch.randn(T, N).to(dt), torch.randn(N).to(dt)
+    qn, kn = torch.rand(H * d) + 0.5, torch.rand(G * d) + 0.5
+    f, mult = rope_frequencies(rot, 500.0, {"factor": 4.0, "original": 32, "fast": 8.0, "slow": 1.0}) if rot else (torch.zeros(1), 1.0)
+    pos = torch.tensor([0, 1, 2, 40, 41, 999, 5, 6, 7], dtype=torch.int32)
+    slots = torch.tensor([0, 1, 2, 9, 10, -1, 7, 12, 13])
+    lam = torch.tensor([0.3])
+    res = []
+    for dev in ("cpu", "cuda"):
+        c1, c2 = torch.zeros(5, bs + PS, G * (d + e), dtype=dt, device=dev), torch.zeros(5, bs + PS, G * (d + e), dtype=dt, device=dev)
+        vf = torch.zeros(T, G * e, dtype=dt, device=dev)
+        mv = lambda t: t.to(dev)
+        q1 = W.window_qkv_write(mv(qkv), mv(bias), mv(qn), mv(kn), H, G, d, e, rot, mv(f), mult, 1e-5, mv(pos), mv(slots), c1, bs, vf, 1, None)
+        q2 = W.window_qkv_write(mv(qkv.flip(0)), mv(bias), mv(qn), mv(kn), H, G, d, e, rot, mv(f), mult, 1e-5, mv(pos), mv(slots), c2, bs, vf, 2, mv(lam))
+        res.append([t.float().cpu() for t in (q1, q2, c1, c2, vf)])
+    for a, b in zip(*res):
+        assert torch.allclose(a, b, atol=tol(dt) * 4, rtol=tol(dt))
+
+
+def _cache_on_gpu(k, v, bs, P, table, pages, dt):
+    """Token rows written directly, pooled rows by the pool kernel in two launches (blocks whose tokens arrive in
+    different steps)."""
+    from llmctl_b200.ops import window_attention as W
+    n, G, d = k.shape
+    e = v.shape[2]
+    PS = W.pooled_rows_per_page(bs, P)
+    cache = torch.zeros(pages, bs + PS, G * (d + e), dtype=dt, device="cuda")
+    rows = torch.tensor([table[j // bs] * (bs + PS) + j % bs for j in range(n)], device="cuda")
+    cache.view(-1, G * (d + e))[rows] = torch.cat([k.reshape(n, -1), v.reshape(n, -1)], -1).to(dt).cuda()
+    tb = torch.tensor([table], dtype=torch.int32, device="cuda")
+    slots = torch.tensor([table[j // bs] * bs + j % bs for j in range(n)], device="cuda")
+    pos = torch.arange(n, dtype=torch.int32, device="cuda")
+    cut = n // 2 + 1
+    for a, b in ((0, cut), (cut, n)):
+        W.window_pool_update(cache, pos[a:b].contiguous(), slots[a:b].contiguous(), torch.zeros(b - a, dtype=torch.int32, device="cuda"), tb, bs, P)
+    return cache
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("H,G,d,e,S,P,bs", [(4, 2, 6, 5, 10, 4, 8), (4, 4, 64, 48, 36, 6, 64), (3, 1, 8, 8, 7, 3, 16), (16, 4, 128, 128, 33, 16, 64),
+                                            (64, 8, 16, 128, 5, 1, 16), (6, 3, 20, 12, 9, 12, 8), (2, 2, 4, 4, 1, 2, 4), (8, 2, 32, 64, 0, 0, 16)])
+def test_attention_kernel_against_oracle(cuda_device, dt, H, G, d, e, S, P, bs):
+    """Whole-prompt tiles, a prompt cut at odd places and single decoded tokens, at sizes that make the kernel take 16, 4
+    and 1 tokens per CTA; pools that do not divide the page or exceed it; no window at all."""
+    from llmctl_b200.ops import window_attention as W
+    from llmctl_b200.serve.ragged import Portion, RaggedBatch
+    torch.manual_seed(2)
+    n = 150
+    k, v, q = torch.randn(n, G, d).to(dt).float(), torch.randn(n, G, e).to(dt).float(), torch.randn(n, H, d)
+    temp, talk = torch.rand(H) + 0.5, torch.eye(H) + torch.randn(H, H) / H
+    pages = (n + bs - 1) // bs
+    table = torch.randperm(pages + 3).tolist()[:pages]
+    cache = _cache_on_gpu(k, v, bs, P or 1, table, pages + 3, dt) if S else _cache_on_gpu(k, v, bs, 1, table, pages + 3, dt)[:, :bs].contiguous()
+    rnd = (lambda z: z.to(dt).double()) if dt != torch.float32 else (lambda z: z)
+    ref = oracle.attend(q.double(), k.double(), v.double(), S or None, P or None, 0.3, temp.double(), talk.double(), rnd).reshape(n, H * e)
+    scale = ref.abs().max().item()
+    dev = torch.device("cuda")
+
+    def run(portions, tile_tokens, rows):
+        b = RaggedBatch(portions, bs, dev)
+        return W.pooled_window_attention(q.reshape(n, H * d)[rows].contiguous().cuda(), cache, b.block_tables, b.tiles(16), tile_tokens,
+                                         b.positions, temp.cuda(), talk.cuda(), 0.3, H, G, d, e, S, P, bs, dt).float().cpu()
+    got = run([Portion(1, [0] * n, 0, [], table)], 16, slice(0, n))
+    assert (got.double() - ref).abs().max().item() <= tol(dt) * max(scale, 1.0), "whole prompt"
+    a, bnd = 37, 101                                                   # a portion in the middle, two sequences side by side
+    got = run([Portion(1, [0] * (bnd - a), a, [], table), Portion(2, [0] * 21, 0, [], table)], 16, list(range(a, bnd)) + list(range(21)))
+    assert (got.double() - torch.cat([ref[a:bnd], ref[:21]])).abs().max().item() <= tol(dt) * max(scale, 1.0), "portions"
+    where = [0, 1, max(S - 1, 0), S, S + max(P, 1) - 1, S + max(P, 1), 63, 64, n - 1]
+    got = run([Portion(10 + i, [0], i, [], table) for i in where], 1, where)
+    assert (got.double() - ref[where]).abs().max().item() <= tol(dt) * max(scale, 1.0), "decode"
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+def test_window_edge_and_pool_edge_decide_on_gpu(cuda_device, dt):
+    """The dominant key of ``test_teluzen_cpu.test_window_edge_and_pool_edge_decide`` on the kernel: last position inside the
+    window, invisible until its block is wholly before the window, then seen through the block's mean; in decode tiles and
+    as part of a prompt tile, with the key at page borders and far back."""
+    from llmctl_b200.ops import window_attention as W
+    from llmctl_b200.serve.ragged import Portion, RaggedBatch
+    torch.manual_seed(3)
+    S, P, bs, d, e = 9, 4, 8, 4, 3
+    dev = torch.device("cuda")
+    for far in (0, 7, 8, 23, 24, 63, 64, 200):
+        n = far + S + 2 * P + 2
+        q, k, v = _decisive(n, far, d, e)
+        v = v.to(dt).float()
+        pages = (n + bs - 1) // bs
+        table = torch.randperm(pages + 2).tolist()[:pages]
+        cache = _cache_on_gpu(k, v, bs, P, table, pages + 2, dt)
+        block_end = far // P * P + P - 1
+        qs = q.reshape(1, d).expand(n - far, d).contiguous().cuda()
+        for mode in ("decode", "prompt"):
+            if mode == "decode":
+                b = RaggedBatch([Portion(i, [0], i, [], table) for i in range(far, n)], bs, dev)
+            else:
+                b = RaggedBatch([Portion(1, [0] * (n - far), far, [], table)], bs, dev)
+            out = W.pooled_window_attention(qs, cache, b.block_tables, b.tiles(16), 1 if mode == "decode" else 16, b.positions, None, None,
+                                            1.0, 1, 1, d, e, S, P, bs, dt).float().cpu()
+            for r, i in enumerate(range(far, n)):
+                if i - far < S:
+                    assert torch.allclose(out[r], v[far, 0], atol=2e-2), f"{mode}, far {far}: inside the window at {i}"
+                elif block_end <= i - S:
+                    blk = v[far // P * P: far // P * P + P, 0].mean(0)
+                    assert torch.allclose(out[r], blk, atol=2e-2), f"{mode}, far {far}: through its block at {i}"
+                else:
+                    assert (out[r] - v[far, 0]).abs().max() > 0.05 and (out[r].abs() < 4).all(), f"{mode}, far {far}: invisible at {i}"
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("T,E,top", [(70, 5, 2), (3, 8, 1), (200, 3, 3), (300, 12, 4)])
+def test_chosen_logit_routing_and_moe(cuda_device, dt, T, E, top):
+    from llmctl_b200.models.ffn import GatedExpertMoE
+    from llmctl_b200.ops import moe as M
+    torch.manual_seed(4)
+    Wd, ff, sf = 64, 24, 40
+    mlp = {"kind": "moe", "router": {"experts": E, "top": top}, "expert": {"ff": ff}, "shared": {"ff": sf}}
+    p = {"router": (torch.randn(E, Wd) * 2).to(torch.bfloat16).float()}
+    for n in [f"e{e}." for e in range(E)] + ["shared."]:
+        f_ = sf if n == "shared." else ff
+        for nm, shp in (("gate", (f_, Wd)), ("up", (f_, Wd)), ("down", (Wd, f_))):
+            p[n + nm] = (torch.randn(*shp) / shp[1] ** 0.5).to(torch.bfloat16).float()
+    x = torch.randn(T, Wd).to(dt)
+    ids, wts, _, _ = M.route(x.float().cuda(), p["router"].to(dt).cuda(), top, softmax=2)
+    oi, ow = oracle.route(x.double(), p["router"].double(), top)
+    z = x.double() @ p["router"].double().T
+    srt = z.sort(-1, descending=True).values
+    clear = (srt[:, top - 1] - srt[:, top]) > 1e-3 if top < E else torch.ones(T, dtype=torch.bool)
+    assert torch.equal(ids.cpu().long()[clear], oi[clear]) and torch.allclose(wts.cpu().double()[clear], ow[clear], atol=1e-5)
+    m = GatedExpertMoE(Wd, E, top, ff, sf, dt, "cuda", scale_input=False, softmax_scores=2, shared_gate=False)
+    m.load(lambda k: p[k].cuda(), "")
+    got = m(x.cuda(), x.float().cuda()).cpu().double()
+    ref = oracle.moe_ff(x.double(), mlp, {k: v.double() for k, v in p.items()}, "")
+    err = (got - ref)[clear].abs().max().item()
+    assert err <= (1e-4 if dt == torch.float32 else 6e-2), err
+
+
+GPU_CONFIGS = {
+    "default": (dict(), 8),
+    "odd_sizes": (dict(width=40, heads=6, kv_heads=3, dim=6, vdim=5, rot_dims=2, window=7, pool=3, ff=33, experts=3, top=1, expert_ff=9,
+                       shared_ff=None, pattern="MD-M", v_mix="1011", yarn=False), 16),
+    "wide_heads": (dict(width=128, heads=16, kv_heads=4, dim=64, vdim=64, rot_dims=32, window=24, pool=8, ff=256, experts=6, top=2,
+                        expert_ff=64, shared_ff=96, pattern="DM", v_mix="11"), 64),
+    "pool_of_one": (dict(heads=3, kv_heads=3, dim=8, vdim=4, rot_dims=4, window=9, pool=1, pattern="DD", v_mix="11"), 32),
+}
+
+
+@pytest.mark.parametrize("name", sorted(GPU_CONFIGS))
+@pytest.mark.parametrize("dt", DTYPES)
+def test_model_matches_oracle_on_gpu(cuda_device, dt, name):
+    """Whole prompt, then portions + token-by-token decoding of the same prompt through the paged cache next to a second
+    request in the same batches, against the oracle's logits."""
+    kw, bs = GPU_CONFIGS[name]
+    cfg = small_cfg(**kw)
+    w = oracle.random_weights(cfg, seed=3)
+    torch.manual_seed(5)
+    toks = torch.randint(0, cfg["vocab"], (75,)).tolist()
+    ref = ref_logits(cfg, w, toks)
+    flips = []
+
+    def same(a, b):
+        if dt == torch.float32:
+            return (a - b).abs().max().item() < 3e-4
+        # bf16, tiny widths: rounding is a few % of a row's rms.  A router logit that is a near tie in fp32 may pick another
+        # expert after rounding and move one token's logits as a whole: at most two such rows per scenario.
+        err = (a - b).pow(2).mean(-1).sqrt() / b.pow(2).mean(-1).sqrt()
+        flips.extend(err[err >= 0.15].tolist())
+        return len(flips) <= 2 and float(err[err < 0.15].mean() if (err < 0.15).any() else 0.0) < 0.05
+    eng = make_engine(cfg, w, dt, "cuda", blocks=max(4, 192 // bs), bs=bs)
+    assert eng.kv.allocate(1, len(toks))
+    got = eng.forward_portions([eng.portion(1, toks, 0, list(range(len(toks))))]).float().cpu()
+    assert same(got, ref)
+    eng.kv.free(1)
+    other = toks[10:40]
+    ref2 = ref_logits(cfg, w, other)
+    cuts, at, at2 = [16, 2, 30] + [1] * 27, 0, 0
+    for c in cuts:
+        ps = []
+        assert eng.kv.allocate(2, at + c)
+        ps.append(eng.portion(2, toks[at:at + c], at, list(range(c))))
+        c2 = min(3, len(other) - at2)
+        if c2 > 0:
+            assert eng.kv.allocate(3, at2 + c2)
+            ps.append(eng.portion(3, other[at2:at2 + c2], at2, list(range(c2))))
+        lg = eng.forward_portions(ps).float().cpu()
+        assert same(lg[:c], ref[at:at + c])
+        if c2 > 0:
+            assert same(lg[c:], ref2[at2:at2 + c2])
+        at, at2 = at + c, at2 + max(c2, 0)
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+def test_greedy_generation_with_replayed_decode_graph(cuda_device, dt):
+    """``InferenceEngine.generate`` with the decode step replayed as a CUDA graph (padded batch, fixed buffers): unequal
+    requests, block growth across pages, windows and pooled blocks passing over decoded tokens; tokens = the oracle's argmax."""
+    from llmctl_b200.serve.engine import InferenceEngine
+    cfg = small_cfg(window=9, pool=4, pattern="DMD", v_mix="011")
+    w = oracle.random_weights(cfg, seed=21)
+    eng = InferenceEngine(copy.deepcopy(cfg), max_batch_size=4, max_batch_tokens=1024, device="cuda", kv_block_size=16, num_kv_blocks=40,
+                          dtype=dt, kv_watermark=0.0, cuda_graphs=True)
+    eng.model.load_state(w)
+    g = torch.Generator().manual_seed(7)
+    prompts = [torch.randint(0, cfg["vocab"], (n,), generator=g).tolist() for n in (5, 30, 1)]
+    seqs = [eng.add_request(p, max_tokens=m, temperature=0.0) for p, m in zip(prompts, (50, 20, 35))]
+    while eng.has_work():
+        eng.step()
+    assert any(k[0] == "ragged" for k in eng._graphs if isinstance(k[0], str)), "the decode graph was never used"
+    gap = 1e-3 if dt == torch.float32 else 0.15
+    for p, s in zip(prompts, seqs):
+        o = s.generated
+        ref = ref_logits(cfg, w, p + o)
+        top2 = ref.topk(2, -1).values
+        for k, tok in enumerate(o):
+            row = len(p) + k - 1
+            if top2[row, 0] - top2[row, 1] > gap:
+                assert tok == int(ref[row].argmax()), f"token {k} of prompt len {len(p)}"
+    assert eng.kv.free_blocks == 40
