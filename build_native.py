@@ -40,7 +40,7 @@ CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall", "-I",
 #: sub-directories (or single files) of csrc/ per component; None = everything
 COMPONENTS = {
     "serve": ["common", "gemm", "norm", "rope", "swiglu", "activation", "moe", "serve", "attention/latent_attention.cu", "attention/latent_attention_t5.cu",
-              "attention/pooled_window_attention.cu",
+              "attention/pooled_window_attention.cu", "attention/pooled_window_attention_mma.cu",
               "comm/watchdog.cu"],      # the gated GEMM modes report expired flag waits through the watchdog
     "all": None,
 }

@@ -27,6 +27,7 @@
 
 #include "../common/dtype.cuh"
 #include "../rope/rope_interleaved.cuh"
+#include "pooled_window.cuh"
 
 namespace llmctl {
 
@@ -87,17 +88,6 @@ window_qkv_write_kernel(const T* __restrict__ qkv, long long ld, const T* __rest
     if (v_mode == 2) v = (1.f - l) * v + l * to_f32(v_first[t * Nv + c]);
     if (crow) crow[Nk + c] = from_f32<T>(v);
   }
-}
-
-// Row of the pooled entry of block b in the cache (in rows of Wc numbers).
-__device__ __forceinline__ long long pooled_row(const int* __restrict__ table, int b, int P, int bs, int PS) {
-  const long long first = static_cast<long long>(b) * P;
-  const int page = static_cast<int>(first / bs);
-  const int first_b = static_cast<int>((static_cast<long long>(page) * bs + P - 1) / P);   // first block starting in the page
-  return static_cast<long long>(table[page]) * (bs + PS) + bs + (b - first_b);
-}
-__device__ __forceinline__ long long token_row(const int* __restrict__ table, int j, int bs, int PS) {
-  return static_cast<long long>(table[j / bs]) * (bs + PS) + j % bs;
 }
 
 // one CTA per token; only the tokens that end a block do anything

@@ -212,5 +212,6 @@ class PooledWindowAttention(nn.Module):
         wops.window_pool_update(cache, batch.positions, batch.slots, batch.seq_rows, batch.block_tables, bs, pool)
         o = wops.pooled_window_attention(q, cache, batch.block_tables, batch.tiles(self.TILE_TOKENS),
                                          1 if batch.decode_only else self.TILE_TOKENS, batch.positions, self.temp, self.talk,
-                                         s.scale, s.heads, s.kv_heads, s.dim, s.vdim, s.window, pool, bs, h.dtype)
+                                         s.scale, s.heads, s.kv_heads, s.dim, s.vdim, s.window, pool, bs, h.dtype,
+                                         max_context=batch.max_context)
         return ops.linear(o, self.w_o), v_first

@@ -26,6 +26,11 @@ native.register_signature("llmctl_window_qkv_write", [c_void_p, c_ll, c_void_p, 
 native.register_signature("llmctl_window_pool_update", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                                          c_int, c_int, c_int, c_void_p])
 native.register_signature("llmctl_pooled_window_attention_rows", [c_int, c_int, c_int, c_int])
+native.register_signature("llmctl_pooled_window_attention_mma_ok", [c_int, c_int, c_int, c_int, c_int])
+native.register_signature("llmctl_pooled_window_attention_mma", [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p,
+                                                                  c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                                  c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p])
+native._KERNELS_PER_CALL["llmctl_pooled_window_attention_mma"] = 1
 native.register_signature("llmctl_pooled_window_attention", [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p,
                                                               c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
                                                               c_int, c_int, c_void_p, c_int, c_void_p])
@@ -118,18 +123,48 @@ def attention_rows(H: int, d: int, e: int, tile_tokens: int) -> int:
     return int(native.lib().llmctl_pooled_window_attention_rows(H, d, e, tile_tokens))
 
 
+def uses_tensor_cores(dtype: torch.dtype, H: int, G: int, d: int, e: int, tile_tokens: int) -> bool:
+    """bf16 caches whose sizes fit the mma.sync kernel (d a multiple of 16, e of 8, H e <= 2048, shared memory) run on
+    it; fp32 and other sizes run the FMA kernel.  Same rule as llmctl_pooled_window_attention_mma_ok."""
+    if dtype != torch.bfloat16 or not native.has_symbol("llmctl_pooled_window_attention_mma"):
+        return False
+    return bool(native.lib().llmctl_pooled_window_attention_mma_ok(H, G, d, e, tile_tokens))
+
+
+def key_splits(ntiles: int, max_context: int, window: int, pool: int, sms: int = 148) -> int:
+    """Slices to cut every tile's keys into on the tensor-core kernel: with few tiles (a decoding batch) and long
+    contexts the keys are spread over about two CTAs per SM, at least 64 keys per slice."""
+    if not max_context:
+        return 1
+    keys = min(max_context, window) + (max(max_context - window, 0) // pool if pool else 0) if window else max_context
+    return int(max(1, min(2 * sms // max(ntiles, 1), keys // 64, 32)))
+
+
 def pooled_window_attention(q: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor, tiles: torch.Tensor,
                             tile_tokens: int, positions: torch.Tensor, temp: Optional[torch.Tensor], talk: Optional[torch.Tensor],
                             scale: float, H: int, G: int, d: int, e: int, window: int, pool: int, block_size: int,
-                            out_dtype: torch.dtype) -> torch.Tensor:
+                            out_dtype: torch.dtype, tensor_cores: bool = True, max_context: int = 0, splits: int = 0) -> torch.Tensor:
     """q: fp32 [T, H d] (normed, rotated); tiles: int32 [n, 4] = (first token row, tokens <= tile_tokens, block-table
     row, 0), the tokens of a tile being consecutive positions of one sequence; temp: fp32 [H] or None; talk: fp32 [H, H]
-    or None; window 0 = every earlier token and no pooled blocks.  Returns [T, H e] in ``out_dtype``."""
+    or None; window 0 = every earlier token and no pooled blocks.  ``tensor_cores`` False forces the FMA kernel;
+    ``max_context`` (longest context in the batch) lets the tensor-core kernel split the keys when tiles are few.
+    Returns [T, H e] in ``out_dtype``."""
     T = q.shape[0]
     bs, PS = block_size, cache.shape[1] - block_size
     if q.is_cuda:
         assert q.dtype == torch.float32 and q.is_contiguous() and cache.is_contiguous() and cache.dtype == out_dtype
         out = torch.empty(T, H * e, dtype=out_dtype, device=q.device)
+        if tensor_cores and uses_tensor_cores(cache.dtype, H, G, d, e, tile_tokens):
+            n = tiles.shape[0]
+            if not splits:
+                splits = key_splits(n, max_context, window, pool)
+            part_ml = torch.empty(n * splits * H * 32, dtype=torch.float32, device=q.device) if splits > 1 else None
+            part_o = torch.empty(splits * T * H * e, dtype=torch.float32, device=q.device) if splits > 1 else None
+            native.call("llmctl_pooled_window_attention_mma", q.data_ptr(), cache.data_ptr(), block_tables.data_ptr(),
+                        block_tables.shape[1], tiles.data_ptr(), n, int(tile_tokens), positions.data_ptr(), native.ptr(temp),
+                        native.ptr(talk), float(scale), H, G, d, e, int(window), int(pool), bs, PS, out.data_ptr(), int(splits), T,
+                        native.ptr(part_ml), native.ptr(part_o), native.stream_ptr())
+            return out
         native.call("llmctl_pooled_window_attention", q.data_ptr(), cache.data_ptr(), block_tables.data_ptr(), block_tables.shape[1],
                     tiles.data_ptr(), tiles.shape[0], int(tile_tokens), positions.data_ptr(), native.ptr(temp), native.ptr(talk),
                     float(scale), H, G, d, e, int(window), int(pool), bs, PS, out.data_ptr(), _is32(cache), native.stream_ptr())

@@ -1,8 +1,8 @@
-"""Serving throughput of a ragged-batch design (Nafazen) beside the GPT/LLaMA family at equal parameter count:
+"""Serving throughput of a ragged-batch design (Nafazen, Teluzen) beside the GPT/LLaMA family at equal parameter count:
 prefill and decode tokens/s through ``InferenceEngine.generate`` (the scheduler, block manager and step function a
 user gets), random weights, a few layer sizes that resemble real models; plus device-timed runs of the design's own
-attention and grouped-GEMM kernels against the measured roofline.  ``bench.py --arch-compare nafazen`` prints the
-result as one JSON line.
+attention and expert kernels against the measured roofline, next to the GPT family's like kernels.
+``bench.py --arch-compare nafazen|teluzen`` prints the result as one JSON line.
 
 Reference: the reference's serving benchmark is ``llmctl bench e2e`` (reference llmctl/cli/commands/bench.py:98-160)."""
 from __future__ import annotations
@@ -20,6 +20,15 @@ SIZES: Dict[str, Dict[str, Any]] = {
                   experts=8, top=2, expert_ff=2048, shared_ff=2048, pattern="aDbMaDcM"),
     "w4096": dict(width=4096, vocab=32000, heads=32, dim=128, rot_dim=64, vdim=128, kv_rank=512, q_rank=1536, ff=14336,
                   experts=16, top=2, expert_ff=1792, shared_ff=3584, pattern="aDbMaDcM"),
+}
+
+
+TELUZEN_SIZES: Dict[str, Dict[str, Any]] = {
+    # 4 layers: dense, MoE, dense, MoE; windows of 512 tokens + pooled blocks of 16; layers 1 and 3 mix values with layer 1's
+    "w1024": dict(width=1024, vocab=32000, heads=8, kv_heads=2, dim=128, vdim=128, rot_dims=64, window=512, pool=16, ff=4096,
+                  experts=8, top=2, expert_ff=1024, shared_ff=1024, pattern="DMDM", v_mix="0101", max_positions=8192),
+    "w2048": dict(width=2048, vocab=32000, heads=16, kv_heads=4, dim=128, vdim=128, rot_dims=64, window=512, pool=16, ff=8192,
+                  experts=8, top=2, expert_ff=2048, shared_ff=2048, pattern="DMDM", v_mix="0101", max_positions=8192),
 }
 
 
@@ -65,6 +74,24 @@ def _serve(cfg, prompts: List[List[int]], new_tokens: int, block_size: int) -> D
     del eng
     torch.cuda.empty_cache()
     return out
+
+
+def _time_flushed(fn, iters: int = 5) -> float:
+    """Device time of ``fn`` with the L2 flushed (a 256 MB buffer rewritten) before every timed call."""
+    junk = torch.empty(64 << 20, dtype=torch.float32, device="cuda")
+    for _ in range(2):
+        fn()
+    total = 0.0
+    for _ in range(iters):
+        for _ in range(3):              # ~120 us of device work: the host has enqueued fn before the device gets to it
+            junk.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        total += a.elapsed_time(b)
+    return total / iters * 1e-3
 
 
 def _time(fn, iters: int = 10) -> float:
@@ -126,6 +153,66 @@ def _kernels(size: Dict[str, Any], peaks: Dict[str, float]) -> Dict[str, Any]:
     return res
 
 
+def _teluzen_kernels(size: Dict[str, Any], peaks: Dict[str, float]) -> Dict[str, Any]:
+    """The design's own kernels in isolation (bf16): projection post-processing + cache append, pooled-window attention
+    as prefill (2 x 2048 tokens) and as decode (32 sequences at context 4096, L2 flushed before every call), and the
+    mixture-of-experts layer on 4096 tokens."""
+    from ..ops import moe as M
+    from ..ops import native
+    from ..ops import window_attention as WA
+    from ..ops.elementwise import rope_frequencies
+    from .ragged import Portion, RaggedBatch
+    dev = torch.device("cuda")
+    H, G, d, e, S, P = size["heads"], size["kv_heads"], size["dim"], size["vdim"], size["window"], size["pool"]
+    bs, res = 64, {}
+    PS = WA.pooled_rows_per_page(bs, P)
+    Wc = G * (d + e)
+    freq, mult = rope_frequencies(size["rot_dims"], 10000.0, None)
+    freq = freq.to(dev)
+    temp, talk = torch.ones(H, device=dev), (torch.eye(H, device=dev) + 0.1 * torch.randn(H, H, device=dev))
+    for name, nseq, ctx, new in (("prefill", 2, 2048, 2048), ("decode", 32, 4096, 1)):
+        per = (ctx + bs - 1) // bs
+        cache = torch.randn(nseq * per, bs + PS, Wc, device=dev).to(torch.bfloat16)
+        ps = [Portion(i, [0] * new, ctx - new, [], list(range(i * per, (i + 1) * per))) for i in range(nseq)]
+        b = RaggedBatch(ps, bs, dev)
+        T = b.num_tokens
+        q = torch.randn(T, H * d, device=dev)
+        tile_tokens = 1 if new == 1 else 16
+        t = _time_flushed(lambda: WA.pooled_window_attention(q, cache, b.block_tables, b.tiles(16), tile_tokens, b.positions, temp, talk,
+                                                             0.09, H, G, d, e, S, P, bs, torch.bfloat16, max_context=b.max_context))
+        pairs = 0                                   # visible (query, key) pairs per head
+        for i in range(ctx - new, ctx):
+            pairs += min(i + 1, S) + max(i - S + 1, 0) // P
+        pairs *= nseq
+        flops = 2.0 * H * pairs * (d + e)
+        rows = nseq * (min(ctx, S + new - 1) + max(ctx - S, 0) // P)            # cache rows a step has to read at least once
+        bytes_ = rows * Wc * 2 + T * H * (d * 4 + e * 2)
+        res[f"window_attention_{name}"] = {"ms": t * 1e3, "tflops": flops / t / 1e12, "gbs": bytes_ / t / 1e9,
+                                           "frac_of_bf16_peak": flops / t / 1e12 / peaks["bf16_tflops"],
+                                           "frac_of_hbm": bytes_ / t / 1e9 / peaks["hbm_gbs"],
+                                           "tensor_cores": WA.uses_tensor_cores(torch.bfloat16, H, G, d, e, tile_tokens)}
+        if new > 1:
+            qkv = torch.randn(T, (H + G) * d + G * e, device=dev).to(torch.bfloat16)
+            bias = torch.zeros((H + G) * d + G * e, device=dev, dtype=torch.bfloat16)
+            nw_q, nw_k = torch.ones(H * d, device=dev), torch.ones(G * d, device=dev)
+            t = _time_flushed(lambda: WA.window_qkv_write(qkv, bias, nw_q, nw_k, H, G, d, e, size["rot_dims"], freq, mult, 1e-5, b.positions,
+                                                          b.slots, cache, bs))
+            bytes_ = T * (((H + G) * d + G * e) * 2 + H * d * 4 + Wc * 2)
+            res["window_qkv_write_prefill"] = {"ms": t * 1e3, "gbs": bytes_ / t / 1e9, "frac_of_hbm": bytes_ / t / 1e9 / peaks["hbm_gbs"]}
+    W, E, top, F = size["width"], size["experts"], size["top"], size["expert_ff"]
+    T = 4096
+    x = torch.randn(T, W, device=dev)
+    wr = torch.randn(E, W, device=dev).to(torch.bfloat16)
+    wgu = (torch.randn(E, 2 * F, W, device=dev) / W ** 0.5).to(torch.bfloat16)
+    wd = (torch.randn(E, W, F, device=dev) / F ** 0.5).to(torch.bfloat16)
+    t = _time(lambda: M.moe_ffn(x, torch.bfloat16, wr, wgu, wd, top, scale_input=False, softmax=2), 5)
+    flops = 2.0 * T * top * 3 * F * W
+    res["moe_ffn_4096_tokens"] = {"ms": t * 1e3, "tflops": flops / t / 1e12, "frac_of_bf16_peak": flops / t / 1e12 / peaks["bf16_tflops"]}
+    res.update(_gpt_kernels(size, peaks))
+    res["native_launches"] = native.launch_count
+    return res
+
+
 def _gpt_kernels(size: Dict[str, Any], peaks: Dict[str, float]) -> Dict[str, Any]:
     """The GPT family's like kernels at like sizes: causal flash attention over the same 2 x 2048 tokens, paged decode
     attention over the same 32 contexts of 4096 (head size 128 for both), and the SwiGLU feed-forward's two GEMMs on
@@ -160,22 +247,28 @@ def _gpt_kernels(size: Dict[str, Any], peaks: Dict[str, float]) -> Dict[str, Any
 
 
 def run(which: str = "nafazen", sizes: List[str] | None = None, prompt_len: int = 1024, batch: int = 8, new_tokens: int = 64) -> Dict[str, Any]:
-    assert which == "nafazen"
-    from ..models.nafazen import NafazenConfig, example_config
+    if which == "nafazen":
+        from ..models.nafazen import NafazenConfig as Config, example_config
+        table, kernels = SIZES, _kernels
+    elif which == "teluzen":
+        from ..models.teluzen import TeluzenConfig as Config, example_config
+        table, kernels = TELUZEN_SIZES, _teluzen_kernels
+    else:
+        raise ValueError(f"no architecture comparison for {which!r}")
     peaks = _peaks()
     out: Dict[str, Any] = {"metric": "serving_tokens_per_s", "design": which, "dtype": "bf16", "data": "synthetic, random weights",
                            "workload": {"prompts": batch, "prompt_len": prompt_len, "new_tokens": new_tokens}, "peaks": peaks, "sizes": {}}
     g = torch.Generator().manual_seed(0)
-    for name in sizes or list(SIZES):
-        size = SIZES[name]
-        ncfg = NafazenConfig.from_dict(example_config(**size), name=f"nafazen-{name}")
+    for name in sizes or list(table):
+        size = table[name]
+        ncfg = Config.from_dict(example_config(**size), name=f"{which}-{name}")
         params = ncfg.num_parameters()
         gcfg = _gpt_equal(ncfg, params)
         prompts = [torch.randint(0, 32000, (prompt_len,), generator=g).tolist() for _ in range(batch)]
         t0 = time.time()
         row = {"params": params, "gpt_params": gcfg.num_parameters(), "gpt_ffn": gcfg.ffn,
-               "nafazen": _serve(ncfg, prompts, new_tokens, 64), "gpt": _serve(gcfg, prompts, new_tokens, 16),
-               "kernels": _kernels(size, peaks)}
+               which: _serve(ncfg, prompts, new_tokens, 64), "gpt": _serve(gcfg, prompts, new_tokens, 16),
+               "kernels": kernels(size, peaks)}
         row["seconds"] = round(time.time() - t0, 1)
         out["sizes"][name] = row
     return out

@@ -288,6 +288,13 @@ int llmctl_pooled_window_attention(const float* q, const void* cache, const int*
                                    const int* tiles, int ntiles, int tile_tokens, const int* positions, const float* temp,
                                    const float* talk, float scale, int H, int G, int d, int e, int S, int P, int bs, int PS,
                                    void* out, int is_fp32, void* stream);
+/* The same on mma.sync tensor cores (bf16 cache and output); _ok says whether the sizes fit. */
+int llmctl_pooled_window_attention_mma_ok(int H, int G, int d, int e, int tile_tokens);
+int llmctl_pooled_window_attention_mma(const float* q, const void* cache, const int* block_tables, int max_blocks,
+                                       const int* tiles, int ntiles, int tile_tokens, const int* positions,
+                                       const float* temp, const float* talk, float scale, int H, int G, int d, int e, int S,
+                                       int P, int bs, int PS, void* out, int splits, int tokens, float* part_ml,
+                                       float* part_o, void* stream);
 
 #ifdef __cplusplus
 }

@@ -86,14 +86,16 @@ def _cache_on_gpu(k, v, bs, P, table, pages, dt):
     return cache
 
 
-@pytest.mark.parametrize("dt", DTYPES)
-@pytest.mark.parametrize("H,G,d,e,S,P,bs", [(4, 2, 6, 5, 10, 4, 8), (4, 4, 64, 48, 36, 6, 64), (3, 1, 8, 8, 7, 3, 16), (16, 4, 128, 128, 33, 16, 64),
+@pytest.mark.parametrize("dt", DTYPES + ["bf16_fma"])
+@pytest.mark.parametrize("H,G,d,e,S,P,bs", [(4, 2, 6, 5, 10, 4, 8), (4, 2, 16, 8, 10, 4, 8), (32, 8, 64, 64, 44, 4, 32), (8, 8, 32, 128, 21, 5, 16), (4, 4, 64, 48, 36, 6, 64), (3, 1, 8, 8, 7, 3, 16), (16, 4, 128, 128, 33, 16, 64),
                                             (64, 8, 16, 128, 5, 1, 16), (6, 3, 20, 12, 9, 12, 8), (2, 2, 4, 4, 1, 2, 4), (8, 2, 32, 64, 0, 0, 16)])
 def test_attention_kernel_against_oracle(cuda_device, dt, H, G, d, e, S, P, bs):
     """Whole-prompt tiles, a prompt cut at odd places and single decoded tokens, at sizes that make the kernel take 16, 4
     and 1 tokens per CTA; pools that do not divide the page or exceed it; no window at all."""
     from llmctl_b200.ops import window_attention as W
     from llmctl_b200.serve.ragged import Portion, RaggedBatch
+    tc = dt != "bf16_fma"                       # bf16 runs the mma.sync kernel where the sizes fit; "bf16_fma" forces the FMA kernel
+    dt = torch.bfloat16 if dt == "bf16_fma" else dt
     torch.manual_seed(2)
     n = 150
     k, v, q = torch.randn(n, G, d).to(dt).float(), torch.randn(n, G, e).to(dt).float(), torch.randn(n, H, d)
@@ -106,10 +108,13 @@ def test_attention_kernel_against_oracle(cuda_device, dt, H, G, d, e, S, P, bs):
     scale = ref.abs().max().item()
     dev = torch.device("cuda")
 
-    def run(portions, tile_tokens, rows):
+    def run(portions, tile_tokens, rows, splits=1):
         b = RaggedBatch(portions, bs, dev)
         return W.pooled_window_attention(q.reshape(n, H * d)[rows].contiguous().cuda(), cache, b.block_tables, b.tiles(16), tile_tokens,
-                                         b.positions, temp.cuda(), talk.cuda(), 0.3, H, G, d, e, S, P, bs, dt).float().cpu()
+                                         b.positions, temp.cuda(), talk.cuda(), 0.3, H, G, d, e, S, P, bs, dt, tensor_cores=tc,
+                                         splits=splits).float().cpu()
+    if (H, d, e) in ((4, 64, 48), (16, 128, 128), (8, 32, 128)):
+        assert W.uses_tensor_cores(torch.bfloat16, H, G, d, e, 16) and W.uses_tensor_cores(torch.bfloat16, H, G, d, e, 1)
     got = run([Portion(1, [0] * n, 0, [], table)], 16, slice(0, n))
     assert (got.double() - ref).abs().max().item() <= tol(dt) * max(scale, 1.0), "whole prompt"
     a, bnd = 37, 101                                                   # a portion in the middle, two sequences side by side
@@ -118,17 +123,24 @@ def test_attention_kernel_against_oracle(cuda_device, dt, H, G, d, e, S, P, bs):
     where = [0, 1, max(S - 1, 0), S, S + max(P, 1) - 1, S + max(P, 1), 63, 64, n - 1]
     got = run([Portion(10 + i, [0], i, [], table) for i in where], 1, where)
     assert (got.double() - ref[where]).abs().max().item() <= tol(dt) * max(scale, 1.0), "decode"
+    if tc and W.uses_tensor_cores(dt, H, G, d, e, 1):           # keys cut into slices with a CTA each, more slices than key tiles too
+        for sp in (2, 3, 7):
+            got = run([Portion(10 + i, [0], i, [], table) for i in where], 1, where, sp)
+            assert (got.double() - ref[where]).abs().max().item() <= tol(dt) * max(scale, 1.0), f"decode, {sp} key slices"
+        got = run([Portion(1, [0] * (bnd - a), a, [], table), Portion(2, [0] * 21, 0, [], table)], 16, list(range(a, bnd)) + list(range(21)), 3)
+        assert (got.double() - torch.cat([ref[a:bnd], ref[:21]])).abs().max().item() <= tol(dt) * max(scale, 1.0), "portions, 3 key slices"
 
 
 @pytest.mark.parametrize("dt", DTYPES)
-def test_window_edge_and_pool_edge_decide_on_gpu(cuda_device, dt):
+@pytest.mark.parametrize("d,e", [(4, 3), (16, 8)])
+def test_window_edge_and_pool_edge_decide_on_gpu(cuda_device, dt, d, e):
     """The dominant key of ``test_teluzen_cpu.test_window_edge_and_pool_edge_decide`` on the kernel: last position inside the
     window, invisible until its block is wholly before the window, then seen through the block's mean; in decode tiles and
     as part of a prompt tile, with the key at page borders and far back."""
     from llmctl_b200.ops import window_attention as W
     from llmctl_b200.serve.ragged import Portion, RaggedBatch
     torch.manual_seed(3)
-    S, P, bs, d, e = 9, 4, 8, 4, 3
+    S, P, bs = 9, 4, 8                           # (d, e) = (16, 8) in bf16 is the mma.sync kernel, the rest the FMA kernel
     dev = torch.device("cuda")
     for far in (0, 7, 8, 23, 24, 63, 64, 200):
         n = far + S + 2 * P + 2
