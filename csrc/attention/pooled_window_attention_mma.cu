@@ -93,7 +93,8 @@ pooled_window_attention_mma_kernel(const PwaMmaParams p) {
   for (int i = tid; i < p.qrows * H * d; i += nthreads) {
     const int r = i / (H * d), c = i % (H * d);
     float v = 0.f;
-    if (r < nq) v = p.q[static_cast<long long>(t0 + r) * H * d + c] * (p.scale * (p.temp ? p.temp[c / d] : 1.f));
+    // scores are kept in units of ln 2 (log2(e) folded into the query scaling), so that every exponential is one exp2f
+    if (r < nq) v = p.q[static_cast<long long>(t0 + r) * H * d + c] * (p.scale * (p.temp ? p.temp[c / d] : 1.f) * 1.4426950408889634f);
     const __nv_bfloat16 hi = __float2bfloat16(v);
     Qhi[r * ldq + c] = hi;
     if (p.qlo) Qlo[r * ldq + c] = __float2bfloat16(v - __bfloat162float(hi));
@@ -126,7 +127,7 @@ pooled_window_attention_mma_kernel(const PwaMmaParams p) {
       float m = -INFINITY, l = 0.f;
       for (int s2 = 0; s2 < p.splits; ++s2) m = fmaxf(m, ml[static_cast<long long>(s2) * H * 16 * 2]);
       if (m > -INFINITY)
-        for (int s2 = 0; s2 < p.splits; ++s2) l += ml[static_cast<long long>(s2) * H * 16 * 2 + 1] * expf(ml[static_cast<long long>(s2) * H * 16 * 2] - m);
+        for (int s2 = 0; s2 < p.splits; ++s2) l += ml[static_cast<long long>(s2) * H * 16 * 2 + 1] * exp2f(ml[static_cast<long long>(s2) * H * 16 * 2] - m);
       sM[i] = m;
       sL[i] = l > 0.f ? 1.f / l : 0.f;
     }
@@ -142,17 +143,18 @@ pooled_window_attention_mma_kernel(const PwaMmaParams p) {
         krow[tid] = k.row;
       }
       __syncthreads();
-      for (int i = tid; i < kMTK * kchunks; i += nthreads) {
-        const int k = i / kchunks, c = i % kchunks;
-        if (k < nk) cp_async_16(Ks + k * ldk + c * 8, p.cache + static_cast<long long>(krow[k]) * Wc + c * 8);
-        else *reinterpret_cast<uint4*>(Ks + k * ldk + c * 8) = make_uint4(0, 0, 0, 0);
-      }
-      if (pass == 1)
-        for (int i = tid; i < kMTK * vchunks; i += nthreads) {
-          const int k = i / vchunks, c = i % vchunks;
-          if (k < nk) cp_async_16(Vs + k * ldv + c * 8, p.cache + static_cast<long long>(krow[k]) * Wc + G * d + c * 8);
-          else *reinterpret_cast<uint4*>(Vs + k * ldv + c * 8) = make_uint4(0, 0, 0, 0);
+      for (int k = warp; k < kMTK; k += p.nwarps) {       // a warp per cache row, a lane per 16-byte piece
+        const __nv_bfloat16* src = p.cache + static_cast<long long>(krow[k]) * Wc;
+        for (int c = lane; c < kchunks; c += 32) {
+          if (k < nk) cp_async_16(Ks + k * ldk + c * 8, src + c * 8);
+          else *reinterpret_cast<uint4*>(Ks + k * ldk + c * 8) = make_uint4(0, 0, 0, 0);
         }
+        if (pass == 1)
+          for (int c = lane; c < vchunks; c += 32) {
+            if (k < nk) cp_async_16(Vs + k * ldv + c * 8, src + G * d + c * 8);
+            else *reinterpret_cast<uint4*>(Vs + k * ldv + c * 8) = make_uint4(0, 0, 0, 0);
+          }
+      }
       cp_async_commit();
       cp_async_wait_all();
       __syncthreads();
@@ -201,14 +203,14 @@ pooled_window_attention_mma_kernel(const PwaMmaParams p) {
             float add = 0.f;
             if (mn > -INFINITY) {
 #pragma unroll
-              for (int nt = 0; nt < kMTK / 8; ++nt) add += expf(sacc[nt][2 * h2] - mn) + expf(sacc[nt][2 * h2 + 1] - mn);
+              for (int nt = 0; nt < kMTK / 8; ++nt) add += exp2f(sacc[nt][2 * h2] - mn) + exp2f(sacc[nt][2 * h2 + 1] - mn);
             }
             add += __shfl_xor_sync(0xffffffffu, add, 1);
             add += __shfl_xor_sync(0xffffffffu, add, 2);
             __syncwarp();
             if (tq == 0 && mn > -INFINITY) {
               sM[g * 16 + r] = mn;
-              sL[g * 16 + r] = l_old * expf(m_old - mn) + add;        // exp(-inf) = 0 at the first tile that shows a key
+              sL[g * 16 + r] = l_old * exp2f(m_old - mn) + add;       // 2^(-inf) = 0 at the first tile that shows a key
             }
           }
         } else {
@@ -219,8 +221,8 @@ pooled_window_attention_mma_kernel(const PwaMmaParams p) {
 #pragma unroll
             for (int nt = 0; nt < kMTK / 8; ++nt) {
               float2 w;
-              w.x = sacc[nt][2 * h2] > -INFINITY ? expf(sacc[nt][2 * h2] - m) * il : 0.f;
-              w.y = sacc[nt][2 * h2 + 1] > -INFINITY ? expf(sacc[nt][2 * h2 + 1] - m) * il : 0.f;
+              w.x = sacc[nt][2 * h2] > -INFINITY ? exp2f(sacc[nt][2 * h2] - m) * il : 0.f;
+              w.y = sacc[nt][2 * h2 + 1] > -INFINITY ? exp2f(sacc[nt][2 * h2 + 1] - m) * il : 0.f;
               *reinterpret_cast<float2*>(Pw + (g * 16 + r) * kPld + nt * 8 + 2 * tq) = w;
             }
           }
