@@ -7,8 +7,8 @@
 Sources are compiled one translation unit per nvcc/g++ process (in parallel) and only when the
 source or a header is newer than the object, so incremental rebuilds take seconds.  ``--components serve``
 builds only what inference needs (GEMMs, norms, rotations, activations, attention over the paged caches,
-mixture-of-experts, sampling); entry points of the parts left out are simply absent from the library
-(``ops.native.has_symbol``), and a later full build adds them.  The reference
+mixture-of-experts, sampling), ``serve-<design>`` only what replaying one design needs; entry points of the parts
+left out are simply absent from the library (``ops.native.has_symbol``), and a later build adds them.  The reference
 has no build system at all — nothing to mirror here.
 """
 from __future__ import annotations
@@ -38,10 +38,14 @@ CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall", "-I",
 
 
 #: sub-directories (or single files) of csrc/ per component; None = everything
+_SERVE_COMMON = ["common", "gemm", "activation", "moe", "comm/watchdog.cu"]    # the gated GEMM modes report expired flag waits through the watchdog
 COMPONENTS = {
-    "serve": ["common", "gemm", "norm", "rope", "swiglu", "activation", "moe", "serve", "attention/latent_attention.cu", "attention/latent_attention_t5.cu",
-              "attention/pooled_window_attention.cu", "attention/pooled_window_attention_mma.cu",
-              "comm/watchdog.cu"],      # the gated GEMM modes report expired flag waits through the watchdog
+    "serve": _SERVE_COMMON + ["norm", "rope", "swiglu", "serve", "attention/latent_attention.cu", "attention/latent_attention_t5.cu",
+                              "attention/pooled_window_attention.cu", "attention/pooled_window_attention_mma.cu"],
+    # what trace replay of one design needs and no more (the library grows when another component is asked for later)
+    "serve-nafazen": _SERVE_COMMON + ["norm/scalar_rmsnorm.cu", "attention/latent_attention.cu", "attention/latent_attention_t5.cu"],
+    "serve-teluzen": _SERVE_COMMON + ["norm/sandwich_norm.cu", "attention/pooled_window_attention.cu",
+                                      "attention/pooled_window_attention_mma.cu"],
     "all": None,
 }
 
@@ -94,8 +98,8 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False, 
     manifest = LIBDIR / "libllmctl_b200.sources"
     linked = set(manifest.read_text().split("\n")) if manifest.exists() and (LIBDIR / "libllmctl_b200.so").exists() else set()
     wanted = {str(p.relative_to(CSRC)) for p in cu_srcs}
-    if wanted < linked:           # a fuller library is there already: keep it whole and refresh what is stale
-        cu_srcs = sorted(CSRC / rel for rel in linked if (CSRC / rel).exists())
+    if linked - wanted:           # the library already holds other parts: keep them, add what is asked for, refresh what is stale
+        cu_srcs = sorted(set(cu_srcs) | {CSRC / rel for rel in linked if rel and (CSRC / rel).exists()})
         wanted = {str(p.relative_to(CSRC)) for p in cu_srcs}
     if cu_srcs:
         if nvcc is None:
