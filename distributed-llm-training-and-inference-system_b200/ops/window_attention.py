@@ -12,6 +12,7 @@ the PyTorch restatement below (CPU tests); on a GPU a missing kernel raises.
 Reference: none — the reference has no attention code (reference llmctl/serve/server.py:199-204)."""
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -127,6 +128,8 @@ def uses_tensor_cores(dtype: torch.dtype, H: int, G: int, d: int, e: int, tile_t
     """bf16 caches whose sizes fit the mma.sync kernel (d a multiple of 16, e of 8, H e <= 2048, shared memory) run on
     it; fp32 and other sizes run the FMA kernel.  Same rule as llmctl_pooled_window_attention_mma_ok."""
     if dtype != torch.bfloat16 or not native.has_symbol("llmctl_pooled_window_attention_mma"):
+        return False
+    if os.environ.get("LLMCTL_WINDOW_ATTENTION", "") == "fma":         # ablation switch: the FMA kernel for bf16 too
         return False
     return bool(native.lib().llmctl_pooled_window_attention_mma_ok(H, G, d, e, tile_tokens))
 
