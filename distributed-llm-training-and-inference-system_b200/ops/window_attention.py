@@ -154,6 +154,7 @@ def pooled_window_attention(q: torch.Tensor, cache: torch.Tensor, block_tables: 
     Returns [T, H e] in ``out_dtype``."""
     T = q.shape[0]
     bs, PS = block_size, cache.shape[1] - block_size
+    window = min(int(window), 1 << 30)            # position + window stays inside int32 in the kernels
     if q.is_cuda:
         assert q.dtype == torch.float32 and q.is_contiguous() and cache.is_contiguous() and cache.dtype == out_dtype
         out = torch.empty(T, H * e, dtype=out_dtype, device=q.device)
