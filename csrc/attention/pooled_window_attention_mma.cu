@@ -136,13 +136,16 @@ pooled_window_attention_mma_kernel(const PwaMmaParams p) {
     for (int u0 = u_begin; u0 < u_end; u0 += kMTK) {
       const int nk = min(kMTK, NU - u0);
       __syncthreads();                                  // the previous tile is done with Ks / Vs / Pw / key rows
+      int all_seen = 1;
       if (tid < kMTK) {
         const WindowKey k = window_key(table, u0 + tid, nb, j0, NU, S, P, bs, PS);
         klo[tid] = k.lo;
         khi[tid] = k.hi;
         krow[tid] = k.row;
+        all_seen = k.lo <= p_first && k.hi >= p_last;
       }
-      __syncthreads();
+      // a tile in the middle of the window (or of the pooled blocks) is seen whole by all 16 tokens: no mask to apply
+      const bool unmasked = __syncthreads_and(all_seen) && nq == 16;
       for (int k = warp; k < kMTK; k += p.nwarps) {       // a warp per cache row, a lane per 16-byte piece
         const __nv_bfloat16* src = p.cache + static_cast<long long>(krow[k]) * Wc;
         for (int c = lane; c < kchunks; c += 32) {
@@ -167,6 +170,7 @@ pooled_window_attention_mma_kernel(const PwaMmaParams p) {
         for (int nt = 0; nt < kMTK / 8; ++nt)
 #pragma unroll
           for (int j = 0; j < 4; ++j) sacc[nt][j] = 0.f;
+#pragma unroll 2
         for (int ks = 0; ks < d; ks += 16) {
           uint32_t ahi[4], alo[4];
           load_q_frag(ahi, Qhi, ldq, nq, zrow, g * d + ks, lane);
@@ -185,10 +189,12 @@ pooled_window_attention_mma_kernel(const PwaMmaParams p) {
         for (int nt = 0; nt < kMTK / 8; ++nt)
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const int r = row + 8 * (j >> 1), k = nt * 8 + 2 * tq + (j & 1);
-            const int pi = p_first + r;
-            const bool seen = r < nq && pi >= klo[k] && pi <= khi[k];
-            sacc[nt][j] = seen ? sacc[nt][j] : -INFINITY;
+            if (!unmasked) {
+              const int r = row + 8 * (j >> 1), k = nt * 8 + 2 * tq + (j & 1);
+              const int pi = p_first + r;
+              const bool seen = r < nq && pi >= klo[k] && pi <= khi[k];
+              sacc[nt][j] = seen ? sacc[nt][j] : -INFINITY;
+            }
             mx[j >> 1] = fmaxf(mx[j >> 1], sacc[nt][j]);
           }
         if (pass == 0) {
@@ -244,6 +250,7 @@ pooled_window_attention_mma_kernel(const PwaMmaParams p) {
           for (int j = 0; j < 8; ++j) a[j] = 0.f;
           const float* base = Pw + row * kPld + ks + 2 * tq;
           if (p.talk) {
+#pragma unroll 4
             for (int g = 0; g < H; ++g) {
               const float tg = sTalk[h * H + g];
               const float* pg = base + g * 16 * kPld;
