@@ -52,14 +52,17 @@ __device__ __forceinline__ uint32_t pack_bf16(__nv_bfloat16 a, __nv_bfloat16 b) 
   return static_cast<uint32_t>(__bfloat16_as_ushort(a)) | (static_cast<uint32_t>(__bfloat16_as_ushort(b)) << 16);
 }
 
-// A fragment of a 16-row query block whose rows >= nq all alias the zero row `zrow` of the shared-memory tile.
-__device__ __forceinline__ void load_q_frag(uint32_t (&a)[4], const __nv_bfloat16* m, int ld, int nq, int zrow, int k0, int lane) {
-  const int r = lane & 15;
-  const __nv_bfloat16* p = m + (r < nq ? r : zrow) * ld + k0 + ((lane >> 4) << 3);
-  const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+// ldmatrix on a shared-memory byte address (the per-lane row addresses are formed once, outside the loops).
+__device__ __forceinline__ void ldsm_x4(uint32_t (&a)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3])
                : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x2(uint32_t (&b)[2], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(b[0]), "=r"(b[1]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x2_trans(uint32_t (&b)[2], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(b[0]), "=r"(b[1]) : "r"(addr));
 }
 
 template <int NT>
@@ -90,14 +93,24 @@ pooled_window_attention_mma_kernel(const PwaMmaParams p) {
   int* krow = khi + kMTK;
 
   const int zrow = p.qrows - 1;
-  for (int i = tid; i < p.qrows * H * d; i += nthreads) {
-    const int r = i / (H * d), c = i % (H * d);
-    float v = 0.f;
-    // scores are kept in units of ln 2 (log2(e) folded into the query scaling), so that every exponential is one exp2f
-    if (r < nq) v = p.q[static_cast<long long>(t0 + r) * H * d + c] * (p.scale * (p.temp ? p.temp[c / d] : 1.f) * 1.4426950408889634f);
-    const __nv_bfloat16 hi = __float2bfloat16(v);
-    Qhi[r * ldq + c] = hi;
-    if (p.qlo) Qlo[r * ldq + c] = __float2bfloat16(v - __bfloat162float(hi));
+  // scores are kept in units of ln 2 (log2(e) folded into the query scaling), so that every exponential is one exp2f
+  for (int r = warp; r < p.qrows; r += p.nwarps) {              // a warp per query row, four numbers per lane and step
+    const float4* src = reinterpret_cast<const float4*>(p.q + static_cast<long long>(t0 + (r < nq ? r : 0)) * H * d);
+#pragma unroll 4
+    for (int c4 = lane; c4 < (H * d) >> 2; c4 += 32) {
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (r < nq) {
+        v = src[c4];
+        const float f = p.scale * (p.temp ? p.temp[(c4 << 2) / d] : 1.f) * 1.4426950408889634f;
+        v.x *= f, v.y *= f, v.z *= f, v.w *= f;
+      }
+      const __nv_bfloat16 h0 = __float2bfloat16(v.x), h1 = __float2bfloat16(v.y), h2 = __float2bfloat16(v.z), h3 = __float2bfloat16(v.w);
+      *reinterpret_cast<uint2*>(Qhi + r * ldq + (c4 << 2)) = make_uint2(pack_bf16(h0, h1), pack_bf16(h2, h3));
+      if (p.qlo)
+        *reinterpret_cast<uint2*>(Qlo + r * ldq + (c4 << 2)) =
+            make_uint2(pack_bf16(__float2bfloat16(v.x - __bfloat162float(h0)), __float2bfloat16(v.y - __bfloat162float(h1))),
+                       pack_bf16(__float2bfloat16(v.z - __bfloat162float(h2)), __float2bfloat16(v.w - __bfloat162float(h3))));
+    }
   }
   for (int i = tid; i < H * 16; i += nthreads) {
     sM[i] = -INFINITY;
@@ -117,6 +130,12 @@ pooled_window_attention_mma_kernel(const PwaMmaParams p) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) oacc[i][j] = 0.f;
 
+  // per-lane ldmatrix addresses (bytes in shared memory): query rows beyond the tile alias the zero row
+  const uint32_t q_lane = ((((lane & 15) < nq ? (lane & 15) : zrow) * ldq + ((lane >> 4) << 3)) << 1);
+  const uint32_t qhi_addr = static_cast<uint32_t>(__cvta_generic_to_shared(Qhi)) + q_lane;
+  const uint32_t qlo_addr = static_cast<uint32_t>(__cvta_generic_to_shared(Qlo)) + q_lane;
+  const uint32_t k_addr = static_cast<uint32_t>(__cvta_generic_to_shared(Ks)) + ((((lane & 7) * ldk) + (((lane >> 3) & 1) << 3)) << 1);
+  const uint32_t v_addr = static_cast<uint32_t>(__cvta_generic_to_shared(Vs)) + (((lane & 15) * ldv) << 1);
   const int kchunks = (G * d) >> 3, vchunks = (G * e) >> 3;      // 16-byte pieces per key / value row
   const int per = ((NU + kMTK - 1) / kMTK + p.splits - 1) / p.splits * kMTK;      // keys per slice, whole tiles
   const int u_begin = split * per, u_end = min(NU, u_begin + per);
@@ -170,15 +189,17 @@ pooled_window_attention_mma_kernel(const PwaMmaParams p) {
         for (int nt = 0; nt < kMTK / 8; ++nt)
 #pragma unroll
           for (int j = 0; j < 4; ++j) sacc[nt][j] = 0.f;
+        const uint32_t qa = qhi_addr + ((g * d) << 1), qb = qlo_addr + ((g * d) << 1), ka = k_addr + ((c * d) << 1);
+        const uint32_t kstep = (8 * ldk) << 1;                      // bytes between n-tiles of 8 keys
 #pragma unroll 2
         for (int ks = 0; ks < d; ks += 16) {
           uint32_t ahi[4], alo[4];
-          load_q_frag(ahi, Qhi, ldq, nq, zrow, g * d + ks, lane);
-          if (p.qlo) load_q_frag(alo, Qlo, ldq, nq, zrow, g * d + ks, lane);
+          ldsm_x4(ahi, qa + (ks << 1));
+          if (p.qlo) ldsm_x4(alo, qb + (ks << 1));
 #pragma unroll
           for (int nt = 0; nt < kMTK / 8; ++nt) {
             uint32_t b[2];
-            load_b_frag_nk(b, Ks, ldk, nt * 8, c * d + ks, lane);
+            ldsm_x2(b, ka + (ks << 1) + nt * kstep);
             mma_bf16_16816(sacc[nt], ahi, b);
             if (p.qlo) mma_bf16_16816(sacc[nt], alo, b);
           }
@@ -278,11 +299,13 @@ pooled_window_attention_mma_kernel(const PwaMmaParams p) {
             ahi[j] = pack_bf16(h0, h1);
             alo[j] = pack_bf16(__float2bfloat16(a[2 * j] - __bfloat162float(h0)), __float2bfloat16(a[2 * j + 1] - __bfloat162float(h1)));
           }
+          const uint32_t va = v_addr + ((ks * ldv + c * e + n_first * 8) << 1);
+          const int n_live = min(NT, (e >> 3) - n_first);          // n-tiles of this unit that exist
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
-            if ((n_first + nt) * 8 >= e) break;
+            if (nt >= n_live) break;
             uint32_t b[2];
-            load_b_frag_kn(b, Vs, ldv, ks, c * e + (n_first + nt) * 8, lane);
+            ldsm_x2_trans(b, va + nt * 16);
             mma_bf16_16816(oacc[iu * NT + nt], ahi, b);
             mma_bf16_16816(oacc[iu * NT + nt], alo, b);
           }
@@ -344,13 +367,15 @@ static size_t pwa_mma_smem(int H, int G, int d, int e, int qrows, int qlo) {
 }
 
 // Output columns per unit (8 * NT, NT in {4, 8, 16}), warps per CTA and units per head for these sizes: a warp holds 16
-// n-tiles of accumulators, i.e. 16 / NT units.  Returns 0 when the sizes do not fit this kernel.
+// n-tiles of accumulators, i.e. up to 16 / NT units.  Returns 0 when the sizes do not fit this kernel.
 static int pwa_mma_plan(int H, int G, int d, int e, int tile_tokens, int* nt_out, int* nwarps, int* chunks, int* qrows, int* qlo) {
   if (H % G || d % 16 || e % 8 || (G * d) % 8 || (G * (d + e)) % 8 || tile_tokens > 16) return 0;
+  // A unit mixes its head's weights itself, so fewer, wider units per head mean less repeated mixing: the widest unit
+  // that still leaves 8 units to spread over the warps; with few heads of few columns, the narrowest.
   int nt = 0, ch = 0;
-  for (int cand : {4, 8, 16}) {                  // the fewest columns per unit for which the warps hold every unit
+  for (int cand : {16, 8, 4}) {
     const int c = (e / 8 + cand - 1) / cand;
-    if (H * c <= 16 * (16 / cand)) {
+    if (H * c <= 16 * (16 / cand) && (H * c >= 8 || cand == 4)) {
       nt = cand;
       ch = c;
       break;
