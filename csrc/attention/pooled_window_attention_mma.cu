@@ -3,7 +3,8 @@
 //
 // CTA = one tile of up to 16 consecutive tokens of a sequence with ALL heads (the mixing of softmax weights across
 // heads needs every head's weight for a key), 4 to 16 warps.  Per tile of 32 keys (pooled rows first, then the window's
-// tokens; rows come straight from the paged cache by 16-byte cp.async):
+// tokens; rows come straight from the paged cache by 16-byte cp.async, into two stages where shared memory allows, so
+// that the next tile's copies fly during this tile's products):
 //   scores   S_g = Q_g K^T for every head g, heads dealt out to the warps: mma.sync m16n8k16, fp32 accumulation.  The
 //            fp32 queries (already scaled by scale * temp[g]) are held as a bf16 pair hi + lo while that fits in shared
 //            memory, so the products are exact to ~2^-17; beyond that size as one bf16.
@@ -36,6 +37,7 @@ struct PwaMmaParams {
   int H, G, d, e, S, P, bs, PS;
   int qrows;        // query rows held in shared memory (tile tokens + one zero row)
   int qlo;          // 1: queries as hi + lo
+  int stages;       // 2: key/value tiles double-buffered, the next tile's copies fly during this tile's products
   int nwarps;
   int chunks;       // blocks of NT * 8 output columns per head
   __nv_bfloat16* out;
@@ -82,15 +84,15 @@ pooled_window_attention_mma_kernel(const PwaMmaParams p) {
   const int ldq = H * d + 8, ldk = G * d + 8, ldv = G * e + 8;
   __nv_bfloat16* Qhi = reinterpret_cast<__nv_bfloat16*>(smem_raw);                 // [qrows][ldq]
   __nv_bfloat16* Qlo = Qhi + (p.qlo ? p.qrows * ldq : 0);                           // [qrows][ldq] when qlo
-  __nv_bfloat16* Ks = Qlo + p.qrows * ldq;                                          // [kMTK][ldk]
-  __nv_bfloat16* Vs = Ks + kMTK * ldk;                                              // [kMTK][ldv]
-  float* Pw = reinterpret_cast<float*>(Vs + kMTK * ldv);                            // [H][16][kPld]
+  __nv_bfloat16* Ks = Qlo + p.qrows * ldq;                                          // [stages][kMTK][ldk]
+  __nv_bfloat16* Vs = Ks + p.stages * kMTK * ldk;                                   // [stages][kMTK][ldv]
+  float* Pw = reinterpret_cast<float*>(Vs + p.stages * kMTK * ldv);                 // [H][16][kPld]
   float* sM = Pw + H * 16 * kPld;                                                   // [H][16]
   float* sL = sM + H * 16;                                                          // [H][16]
   float* sTalk = sL + H * 16;                                                       // [H][H]
-  int* klo = reinterpret_cast<int*>(sTalk + H * H);                                 // [kMTK]
-  int* khi = klo + kMTK;
-  int* krow = khi + kMTK;
+  int* klo = reinterpret_cast<int*>(sTalk + H * H);                                 // [stages][kMTK]
+  int* khi = klo + p.stages * kMTK;
+  int* krow = khi + p.stages * kMTK;
 
   const int zrow = p.qrows - 1;
   // scores are kept in units of ln 2 (log2(e) folded into the query scaling), so that every exponential is one exp2f
@@ -152,34 +154,53 @@ pooled_window_attention_mma_kernel(const PwaMmaParams p) {
     }
   }
   for (int pass = (p.mode == 2 ? 1 : 0); pass < (p.mode == 1 ? 1 : 2); ++pass) {
-    for (int u0 = u_begin; u0 < u_end; u0 += kMTK) {
+    // Tile `it` lives in stage it % stages.  fetch(): visibility and cache rows of the tile's keys, then its copies (one
+    // cp.async group per tile); returns whether all 16 tokens see the whole tile (no mask to apply then).
+    auto fetch = [&](int it, int st) -> bool {
+      const int u0 = u_begin + it * kMTK;
       const int nk = min(kMTK, NU - u0);
-      __syncthreads();                                  // the previous tile is done with Ks / Vs / Pw / key rows
       int all_seen = 1;
       if (tid < kMTK) {
         const WindowKey k = window_key(table, u0 + tid, nb, j0, NU, S, P, bs, PS);
-        klo[tid] = k.lo;
-        khi[tid] = k.hi;
-        krow[tid] = k.row;
+        klo[st * kMTK + tid] = k.lo;
+        khi[st * kMTK + tid] = k.hi;
+        krow[st * kMTK + tid] = k.row;
         all_seen = k.lo <= p_first && k.hi >= p_last;
       }
-      // a tile in the middle of the window (or of the pooled blocks) is seen whole by all 16 tokens: no mask to apply
-      const bool unmasked = __syncthreads_and(all_seen) && nq == 16;
+      const bool whole = __syncthreads_and(all_seen) && nq == 16;
+      __nv_bfloat16* kd = Ks + st * kMTK * ldk;
+      __nv_bfloat16* vd = Vs + st * kMTK * ldv;
       for (int k = warp; k < kMTK; k += p.nwarps) {       // a warp per cache row, a lane per 16-byte piece
-        const __nv_bfloat16* src = p.cache + static_cast<long long>(krow[k]) * Wc;
+        const __nv_bfloat16* src = p.cache + static_cast<long long>(krow[st * kMTK + k]) * Wc;
         for (int c = lane; c < kchunks; c += 32) {
-          if (k < nk) cp_async_16(Ks + k * ldk + c * 8, src + c * 8);
-          else *reinterpret_cast<uint4*>(Ks + k * ldk + c * 8) = make_uint4(0, 0, 0, 0);
+          if (k < nk) cp_async_16(kd + k * ldk + c * 8, src + c * 8);
+          else *reinterpret_cast<uint4*>(kd + k * ldk + c * 8) = make_uint4(0, 0, 0, 0);
         }
         if (pass == 1)
           for (int c = lane; c < vchunks; c += 32) {
-            if (k < nk) cp_async_16(Vs + k * ldv + c * 8, src + G * d + c * 8);
-            else *reinterpret_cast<uint4*>(Vs + k * ldv + c * 8) = make_uint4(0, 0, 0, 0);
+            if (k < nk) cp_async_16(vd + k * ldv + c * 8, src + G * d + c * 8);
+            else *reinterpret_cast<uint4*>(vd + k * ldv + c * 8) = make_uint4(0, 0, 0, 0);
           }
       }
       cp_async_commit();
-      cp_async_wait_all();
+      return whole;
+    };
+    const int n_tiles = u_end > u_begin ? (u_end - u_begin + kMTK - 1) / kMTK : 0;
+    __syncthreads();                                    // the previous pass is done with every stage
+    bool unmasked_next = n_tiles > 0 ? fetch(0, 0) : false;
+    for (int it = 0; it < n_tiles; ++it) {
+      const int st = p.stages == 2 ? (it & 1) : 0;
+      const bool unmasked = unmasked_next;
+      if (p.stages == 2 && it + 1 < n_tiles) {
+        unmasked_next = fetch(it + 1, st ^ 1);          // stage st ^ 1 was released by the barrier that ended tile it - 1
+        cp_async_wait_prior();                          // tile it has landed; tile it + 1 is in flight
+      } else {
+        cp_async_wait_all();
+      }
       __syncthreads();
+      const int* tlo = klo + st * kMTK;
+      const int* thi = khi + st * kMTK;
+      const uint32_t k_stage = k_addr + ((st * kMTK * ldk) << 1), v_stage = v_addr + ((st * kMTK * ldv) << 1);
 
       // ---- scores of the heads this warp is dealt ----
       for (int g = warp; g < H; g += p.nwarps) {
@@ -189,7 +210,7 @@ pooled_window_attention_mma_kernel(const PwaMmaParams p) {
         for (int nt = 0; nt < kMTK / 8; ++nt)
 #pragma unroll
           for (int j = 0; j < 4; ++j) sacc[nt][j] = 0.f;
-        const uint32_t qa = qhi_addr + ((g * d) << 1), qb = qlo_addr + ((g * d) << 1), ka = k_addr + ((c * d) << 1);
+        const uint32_t qa = qhi_addr + ((g * d) << 1), qb = qlo_addr + ((g * d) << 1), ka = k_stage + ((c * d) << 1);
         const uint32_t kstep = (8 * ldk) << 1;                      // bytes between n-tiles of 8 keys
 #pragma unroll 2
         for (int ks = 0; ks < d; ks += 16) {
@@ -213,7 +234,7 @@ pooled_window_attention_mma_kernel(const PwaMmaParams p) {
             if (!unmasked) {
               const int r = row + 8 * (j >> 1), k = nt * 8 + 2 * tq + (j & 1);
               const int pi = p_first + r;
-              const bool seen = r < nq && pi >= klo[k] && pi <= khi[k];
+              const bool seen = r < nq && pi >= tlo[k] && pi <= thi[k];
               sacc[nt][j] = seen ? sacc[nt][j] : -INFINITY;
             }
             mx[j >> 1] = fmaxf(mx[j >> 1], sacc[nt][j]);
@@ -255,7 +276,11 @@ pooled_window_attention_mma_kernel(const PwaMmaParams p) {
           }
         }
       }
-      if (pass == 0) continue;
+      if (pass == 0) {
+        __syncthreads();                                  // the stage is free again
+        if (p.stages == 1 && it + 1 < n_tiles) unmasked_next = fetch(it + 1, 0);
+        continue;
+      }
       __syncthreads();
       // ---- mixed weights x values, one (head, block of NT * 8 output columns) per warp at a time ----
 #pragma unroll
@@ -299,7 +324,7 @@ pooled_window_attention_mma_kernel(const PwaMmaParams p) {
             ahi[j] = pack_bf16(h0, h1);
             alo[j] = pack_bf16(__float2bfloat16(a[2 * j] - __bfloat162float(h0)), __float2bfloat16(a[2 * j + 1] - __bfloat162float(h1)));
           }
-          const uint32_t va = v_addr + ((ks * ldv + c * e + n_first * 8) << 1);
+          const uint32_t va = v_stage + ((ks * ldv + c * e + n_first * 8) << 1);
           const int n_live = min(NT, (e >> 3) - n_first);          // n-tiles of this unit that exist
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
@@ -311,6 +336,8 @@ pooled_window_attention_mma_kernel(const PwaMmaParams p) {
           }
         }
       }
+      __syncthreads();                                    // the stage and the weight tile are free again
+      if (p.stages == 1 && it + 1 < n_tiles) unmasked_next = fetch(it + 1, 0);
     }
     if (pass == 0) {
       __syncthreads();
@@ -360,15 +387,16 @@ pwa_sum_partials_kernel(const float* __restrict__ part, int splits, long long n,
   out[i] = __float2bfloat16(v);
 }
 
-static size_t pwa_mma_smem(int H, int G, int d, int e, int qrows, int qlo) {
-  size_t b = static_cast<size_t>(qrows) * (H * d + 8) * 2 * (qlo ? 2 : 1) + static_cast<size_t>(kMTK) * (G * d + 8 + G * e + 8) * 2;
-  b += (static_cast<size_t>(H) * 16 * kPld + 2ull * H * 16 + static_cast<size_t>(H) * H) * 4 + 3 * kMTK * 4;
+static size_t pwa_mma_smem(int H, int G, int d, int e, int qrows, int qlo, int stages) {
+  size_t b = static_cast<size_t>(qrows) * (H * d + 8) * 2 * (qlo ? 2 : 1) + static_cast<size_t>(stages) * kMTK * (G * d + 8 + G * e + 8) * 2;
+  b += (static_cast<size_t>(H) * 16 * kPld + 2ull * H * 16 + static_cast<size_t>(H) * H) * 4 + 3ull * stages * kMTK * 4;
   return b;
 }
 
 // Output columns per unit (8 * NT, NT in {4, 8, 16}), warps per CTA and units per head for these sizes: a warp holds 16
 // n-tiles of accumulators, i.e. up to 16 / NT units.  Returns 0 when the sizes do not fit this kernel.
-static int pwa_mma_plan(int H, int G, int d, int e, int tile_tokens, int* nt_out, int* nwarps, int* chunks, int* qrows, int* qlo) {
+static int pwa_mma_plan(int H, int G, int d, int e, int tile_tokens, int* nt_out, int* nwarps, int* chunks, int* qrows, int* qlo,
+                        int* stages) {
   if (H % G || d % 16 || e % 8 || (G * d) % 8 || (G * (d + e)) % 8 || tile_tokens > 16) return 0;
   // A unit mixes its head's weights itself, so fewer, wider units per head mean less repeated mixing: the widest unit
   // that still leaves 8 units to spread over the warps; with few heads of few columns, the narrowest.
@@ -388,8 +416,16 @@ static int pwa_mma_plan(int H, int G, int d, int e, int tile_tokens, int* nt_out
   *nwarps = w;
   *chunks = ch;
   *qrows = tile_tokens + 1;
-  *qlo = pwa_mma_smem(H, G, d, e, *qrows, 1) <= 200 * 1024;
-  return pwa_mma_smem(H, G, d, e, *qrows, *qlo) <= 200 * 1024;
+  // shared memory goes to the exact queries first, then to the second key/value stage, unless that stage would cost a
+  // resident CTA (two CTAs that overlap each other's copies beat one CTA that overlaps its own)
+  *qlo = pwa_mma_smem(H, G, d, e, *qrows, 1, 1) <= 200 * 1024;
+  auto resident = [&](int stg) {
+    const int by_smem = static_cast<int>((227 * 1024) / (pwa_mma_smem(H, G, d, e, *qrows, *qlo, stg) + 1024));
+    const int by_regs = 65536 / (w * 32 * 128);
+    return by_smem < by_regs ? by_smem : by_regs;
+  };
+  *stages = (pwa_mma_smem(H, G, d, e, *qrows, *qlo, 2) <= 200 * 1024 && resident(2) >= resident(1)) ? 2 : 1;
+  return pwa_mma_smem(H, G, d, e, *qrows, *qlo, *stages) <= 200 * 1024;
 }
 
 }  // namespace llmctl
@@ -398,8 +434,8 @@ using namespace llmctl;
 
 // 1 if llmctl_pooled_window_attention_mma takes these sizes (bf16 only).
 LLMCTL_API int llmctl_pooled_window_attention_mma_ok(int H, int G, int d, int e, int tile_tokens) {
-  int nt, w, ch, qr, ql;
-  return pwa_mma_plan(H, G, d, e, tile_tokens, &nt, &w, &ch, &qr, &ql);
+  int nt, w, ch, qr, ql, stg;
+  return pwa_mma_plan(H, G, d, e, tile_tokens, &nt, &w, &ch, &qr, &ql, &stg);
 }
 
 // Same arguments as llmctl_pooled_window_attention; cache and out are bf16.  splits > 1 cuts every tile's keys into
@@ -413,12 +449,12 @@ LLMCTL_API int llmctl_pooled_window_attention_mma(const float* q, const void* ca
   LLMCTL_BEGIN();
   LLMCTL_REQUIRE(H > 0 && G > 0 && d > 0 && e > 0 && S >= 0 && (S == 0 || P > 0) && bs > 0 && tile_tokens > 0);
   if (ntiles == 0) return 0;
-  int nt, w, ch, qr, ql;
-  LLMCTL_REQUIRE(pwa_mma_plan(H, G, d, e, tile_tokens, &nt, &w, &ch, &qr, &ql));
+  int nt, w, ch, qr, ql, stg;
+  LLMCTL_REQUIRE(pwa_mma_plan(H, G, d, e, tile_tokens, &nt, &w, &ch, &qr, &ql, &stg));
   PwaMmaParams p{q, (const __nv_bfloat16*)cache, block_tables, max_blocks, tiles, positions, temp, talk, scale, H, G, d, e, S, P, bs, PS,
-                 qr, ql, w, ch, (__nv_bfloat16*)out, splits > 1 ? splits : 1, 0, tokens, part_ml, part_o};
+                 qr, ql, stg, w, ch, (__nv_bfloat16*)out, splits > 1 ? splits : 1, 0, tokens, part_ml, part_o};
   LLMCTL_REQUIRE(splits <= 1 || (part_ml != nullptr && part_o != nullptr && tokens > 0));
-  const size_t smem = pwa_mma_smem(H, G, d, e, qr, ql);
+  const size_t smem = pwa_mma_smem(H, G, d, e, qr, ql, stg);
   cudaStream_t s = (cudaStream_t)stream;
 #define LLMCTL_PWA_LAUNCH(NT)                                                                                              \
   do {                                                                                                                     \
