@@ -4,7 +4,8 @@
 //   llmctl_embed_positions   : x[t] = table[token[t]] + pos_table[position[t]]        (learned absolute positions)
 //   llmctl_rmsnorm_rows      : out[r] = w * x[rows[r]] / sqrt(mean(x[rows[r]]^2) + eps) for all or selected rows
 //   llmctl_sandwich_residual : x += wb * y / sqrt(mean(y^2) + eps), and in the same pass, when w_next is given,
-//                              out = w_next * x / sqrt(mean(x^2) + eps) for the next sublayer
+//                              out = w_next * x / sqrt(mean(x^2) + eps) for the next sublayer (also unrounded in fp32
+//                              when out32 is given: a router reads that)
 //
 // The stream, the sums and the weights are fp32 whatever the activation type; only `y` (a GEMM's output) and `out`
 // (a GEMM's input) have the activation type.  One CTA per row.
@@ -41,7 +42,7 @@ rmsnorm_rows_kernel(const float* __restrict__ x, const long long* __restrict__ r
 template <typename Ty, typename To>
 __global__ void __launch_bounds__(256)
 sandwich_residual_kernel(const Ty* __restrict__ y, long long ldy, float* __restrict__ x, const float* __restrict__ wb,
-                         const float* __restrict__ w_next, To* __restrict__ out, int cols, float eps) {
+                         const float* __restrict__ w_next, To* __restrict__ out, float* __restrict__ out32, int cols, float eps) {
   __shared__ float red[32];
   const long long row = blockIdx.x;
   const Ty* yr = y + row * ldy;
@@ -62,7 +63,11 @@ sandwich_residual_kernel(const Ty* __restrict__ y, long long ldy, float* __restr
   if (!w_next) return;
   sx = block_sum(sx, red);
   const float r2 = 1.f / sqrtf(sx / static_cast<float>(cols) + eps);
-  for (int c = threadIdx.x; c < cols; c += blockDim.x) out[row * cols + c] = from_f32<To>(xr[c] * r2 * w_next[c]);
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    const float v = xr[c] * r2 * w_next[c];
+    out[row * cols + c] = from_f32<To>(v);
+    if (out32) out32[row * cols + c] = v;
+  }
 }
 
 }  // namespace llmctl
@@ -90,20 +95,21 @@ LLMCTL_API int llmctl_rmsnorm_rows(const float* x, const long long* rows, const 
 }
 
 // y: [rows, cols] (fp32 if y_fp32 else bf16, row stride ldy); x: fp32 [rows, cols] updated in place; wb, w_next: fp32
-// [cols]; out: [rows, cols] (fp32 if out_fp32 else bf16), written when w_next is not null.
+// [cols]; out: [rows, cols] (fp32 if out_fp32 else bf16), written when w_next is not null; out32: optional fp32 copy of out
+// before rounding.
 LLMCTL_API int llmctl_sandwich_residual(const void* y, int y_fp32, long long ldy, float* x, const float* wb, const float* w_next,
-                                        void* out, int out_fp32, int rows, int cols, float eps, void* stream) {
+                                        void* out, int out_fp32, float* out32, int rows, int cols, float eps, void* stream) {
   LLMCTL_BEGIN();
   LLMCTL_REQUIRE(cols > 0 && rows >= 0 && ldy >= cols && (w_next == nullptr || out != nullptr));
   if (rows == 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
   if (y_fp32 && out_fp32)
-    sandwich_residual_kernel<float, float><<<rows, 256, 0, s>>>((const float*)y, ldy, x, wb, w_next, (float*)out, cols, eps);
+    sandwich_residual_kernel<float, float><<<rows, 256, 0, s>>>((const float*)y, ldy, x, wb, w_next, (float*)out, out32, cols, eps);
   else if (y_fp32)
-    sandwich_residual_kernel<float, __nv_bfloat16><<<rows, 256, 0, s>>>((const float*)y, ldy, x, wb, w_next, (__nv_bfloat16*)out, cols, eps);
+    sandwich_residual_kernel<float, __nv_bfloat16><<<rows, 256, 0, s>>>((const float*)y, ldy, x, wb, w_next, (__nv_bfloat16*)out, out32, cols, eps);
   else if (out_fp32)
-    sandwich_residual_kernel<__nv_bfloat16, float><<<rows, 256, 0, s>>>((const __nv_bfloat16*)y, ldy, x, wb, w_next, (float*)out, cols, eps);
+    sandwich_residual_kernel<__nv_bfloat16, float><<<rows, 256, 0, s>>>((const __nv_bfloat16*)y, ldy, x, wb, w_next, (float*)out, out32, cols, eps);
   else
-    sandwich_residual_kernel<__nv_bfloat16, __nv_bfloat16><<<rows, 256, 0, s>>>((const __nv_bfloat16*)y, ldy, x, wb, w_next, (__nv_bfloat16*)out, cols, eps);
+    sandwich_residual_kernel<__nv_bfloat16, __nv_bfloat16><<<rows, 256, 0, s>>>((const __nv_bfloat16*)y, ldy, x, wb, w_next, (__nv_bfloat16*)out, out32, cols, eps);
   LLMCTL_RETURN_LAST();
 }

@@ -197,9 +197,15 @@ class TeluzenModel(nn.Module):
         for i, blk in enumerate(blocks):
             after = blocks[i + 1].norm1 if i + 1 < len(blocks) else None        # in-norm of the sublayer that follows
             y, v_first = blk.mixer(h, batch, caches[i], v_first)
-            h = eops.sandwich_residual(y, x, blk.norm1b, blk.norm2 if blk.mlp is not None else after, eps, dt)
-            if blk.mlp is not None:
-                y = blk.mlp(h, h if h.dtype == torch.float32 else h.float())
+            if blk.mlp is None:
+                h = eops.sandwich_residual(y, x, blk.norm1b, after, eps, dt)
+            else:
+                # the feed-forward's input in the activation type and unrounded (the router of a mixture reads the latter)
+                if isinstance(blk.mlp, GatedExpertMoE):
+                    h, h32 = eops.sandwich_residual(y, x, blk.norm1b, blk.norm2, eps, dt, want_fp32=True)
+                else:
+                    h = h32 = eops.sandwich_residual(y, x, blk.norm1b, blk.norm2, eps, dt)
+                y = blk.mlp(h, h32)
                 h = eops.sandwich_residual(y, x, blk.norm2b, after, eps, dt)
             if layer_trace is not None:
                 layer_trace.append(x.clone())

@@ -27,8 +27,8 @@ native.register_signature("llmctl_gated_silu", [c_void_p, c_ll, c_void_p, c_int,
 native.register_signature("llmctl_relu_squared", [c_void_p, c_void_p, c_int, c_ll, c_void_p])
 native.register_signature("llmctl_embed_positions", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p])
 native.register_signature("llmctl_rmsnorm_rows", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
-native.register_signature("llmctl_sandwich_residual", [c_void_p, c_int, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                                                        c_float, c_void_p])
+native.register_signature("llmctl_sandwich_residual", [c_void_p, c_int, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                                                        c_int, c_float, c_void_p])
 
 
 def _is32(t: torch.Tensor) -> int:
@@ -183,18 +183,24 @@ def rmsnorm_rows(x: torch.Tensor, rows: Optional[torch.Tensor], w: torch.Tensor,
 
 
 def sandwich_residual(y: torch.Tensor, x: torch.Tensor, w_out: torch.Tensor, w_next: Optional[torch.Tensor], eps: float,
-                      act_dtype: torch.dtype) -> Optional[torch.Tensor]:
+                      act_dtype: torch.dtype, want_fp32: bool = False):
     """``x += w_out * y / rms(y)`` in place on the fp32 stream; with ``w_next`` also returns ``w_next * x / rms(x)`` of the
-    new stream in ``act_dtype`` (the next sublayer's input) from the same pass.  Weights: fp32 [W]."""
+    new stream in ``act_dtype`` (the next sublayer's input) from the same pass.  Weights: fp32 [W].  ``want_fp32``: returns
+    (input in ``act_dtype``, the same before rounding in fp32) — a router reads the unrounded one."""
     T, W = x.shape
     assert x.dtype == torch.float32 and x.is_contiguous() and y.shape == x.shape and y.stride(1) == 1
     if x.is_cuda:
         out = torch.empty(T, W, dtype=act_dtype, device=x.device) if w_next is not None else None
+        out32 = None
+        if want_fp32 and w_next is not None and act_dtype != torch.float32:
+            out32 = torch.empty(T, W, dtype=torch.float32, device=x.device)
         native.call("llmctl_sandwich_residual", y.data_ptr(), _is32(y), y.stride(0), x.data_ptr(), w_out.data_ptr(), native.ptr(w_next),
-                    native.ptr(out), int(act_dtype == torch.float32), T, W, float(eps), native.stream_ptr())
-        return out
+                    native.ptr(out), int(act_dtype == torch.float32), native.ptr(out32), T, W, float(eps), native.stream_ptr())
+        return (out, out if out32 is None else out32) if want_fp32 else out
     yf = y.float()
     x += yf / torch.sqrt(yf.pow(2).mean(-1, keepdim=True) + eps) * w_out
     if w_next is None:
-        return None
-    return (x / torch.sqrt(x.pow(2).mean(-1, keepdim=True) + eps) * w_next).to(act_dtype)
+        return (None, None) if want_fp32 else None
+    h32 = x / torch.sqrt(x.pow(2).mean(-1, keepdim=True) + eps) * w_next
+    h = h32.to(act_dtype)
+    return (h, h32) if want_fp32 else h

@@ -271,7 +271,7 @@ int llmctl_rmsnorm_rows(const float* x, const long long* rows, const float* w, v
                         float eps, void* stream);
 /* x += wb * y / rms(y) on the fp32 stream; with w_next also out = w_next * x / rms(x) of the new stream. */
 int llmctl_sandwich_residual(const void* y, int y_fp32, long long ldy, float* x, const float* wb, const float* w_next,
-                             void* out, int out_fp32, int rows, int cols, float eps, void* stream);
+                             void* out, int out_fp32, float* out32, int rows, int cols, float eps, void* stream);
 /* Packed projection [q | k | v] -> fp32 queries and the token's cache row: bias, RMS norm over the whole q / k
  * projection, rotation of the first `rot` numbers of every head, value mixing (v_mode 1: publish v_first, 2: blend). */
 int llmctl_window_qkv_write(const void* qkv, long long ld, const void* bias, const float* qn_w, const float* kn_w, int H,

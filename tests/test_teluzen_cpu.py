@@ -60,6 +60,8 @@ def test_sandwich_norm_ops_embedding_and_squared_relu():
     want_x = x + oracle.rms_norm(y, wb, 1e-3)
     h = E.sandwich_residual(y, x, wb, wn, 1e-3, torch.float32)
     assert torch.allclose(x, want_x, atol=1e-6) and torch.allclose(h, oracle.rms_norm(want_x, wn, 1e-3), atol=1e-6)
+    hb, h32 = E.sandwich_residual(y.clone(), x.clone() - oracle.rms_norm(y, wb, 1e-3), wb, wn, 1e-3, torch.bfloat16, want_fp32=True)
+    assert hb.dtype == torch.bfloat16 and torch.allclose(h32, h, atol=1e-6) and torch.equal(hb, h32.to(torch.bfloat16))
     assert E.sandwich_residual(y, x, wb, None, 1e-3, torch.float32) is None
     assert torch.allclose(x, want_x + oracle.rms_norm(y, wb, 1e-3), atol=1e-6)
     assert torch.allclose(E.rmsnorm_rows(x, torch.tensor([4, 1]), wn, 1e-3, torch.float32), oracle.rms_norm(x[[4, 1]], wn, 1e-3), atol=1e-6)

@@ -30,6 +30,9 @@ def test_sandwich_norm_kernels(cuda_device, dt):
         xg = x.cuda()
         hg = E.sandwich_residual(y.cuda(), xg, wb.cuda(), wn.cuda(), 1e-5, dt)
         assert torch.allclose(xg.cpu(), xr, atol=1e-5) and torch.allclose(hg.float().cpu(), hr.float(), atol=tol(dt) * 4)
+        xg2 = x.cuda()
+        h2, h32 = E.sandwich_residual(y.cuda(), xg2, wb.cuda(), wn.cuda(), 1e-5, dt, want_fp32=True)
+        assert torch.equal(h2, hg) and h32.dtype == torch.float32 and torch.equal(h32.to(dt), h2)
         rows = torch.tensor([T - 1, 0])
         a = E.rmsnorm_rows(xg, rows.cuda(), wn.cuda(), 1e-5, dt)
         assert torch.allclose(a.float().cpu(), E.rmsnorm_rows(xr, rows, wn, 1e-5, dt).float(), atol=tol(dt) * 4)
